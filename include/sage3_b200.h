@@ -1,0 +1,148 @@
+/*
+ * C ABI of libsage3_b200.so: NVFP4 (microscaled FP4) attention for NVIDIA B200 (sm_100a).
+ *
+ * Plain pointers and sizes only; no torch / pybind types.  Every function returns a status
+ * (0 = ok, see sage3_status_string) and never throws, aborts or exits.  The library allocates
+ * nothing on the device: the caller owns inputs, outputs and workspace (sage3_buffer_sizes says
+ * how large each one must be).  All work is enqueued on the stream the caller passes
+ * (a cudaStream_t cast to void*; NULL = the legacy default stream) on the current device.
+ *
+ * The entry points stand in for the two CPython extension modules of the reference project
+ * (paths relative to sageattention3_blackwell/sageattn4/):
+ *
+ *   sage3_quant_qkv   <- quantization/fp4_quantization_4d.cu:414-490 scaled_fp4_quant,
+ *                        :492-569 scaled_fp4_quant_permute, :571-648 scaled_fp4_quant_trans
+ *                        (pybind block :650-654), plus the eager preprocessing of
+ *                        api.py:112-205 (K channel-mean removal :184, per-128-token Q mean
+ *                        :26-72,:186-191, delta_s :201, zero padding :196-203)
+ *   sage3_attn_fwd    <- blackwell/api.cpp:258-395 mha_fwd (pybind name "fwd", :399-405)
+ *   sage3_attention   <- api.py:250-288 sageattn4_blackwell without its K-packing steps
+ *                        (= the SageAttention3 call sequence), in one call
+ *
+ * Tensor arguments are bf16 with the last (head_dim) dimension contiguous; batch / head / token
+ * strides are given in elements, so both the "HND" [B,H,N,D] and "NHD" [B,N,H,D] layouts of
+ * sageattention/core.py:79-88 are expressed by strides.  head_dim must be 64 or 128.
+ */
+#ifndef SAGE3_B200_H
+#define SAGE3_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define SAGE3_API __attribute__((visibility("default")))
+#else
+#define SAGE3_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  SAGE3_OK = 0,
+  SAGE3_ERR_ARGUMENT = 1,     /* null pointer, bad size, bad stride, buffer too small            */
+  SAGE3_ERR_UNSUPPORTED = 2,  /* head_dim not in {64,128}, Hq not a multiple of Hkv, ...          */
+  SAGE3_ERR_CUDA = 3,         /* a CUDA runtime / driver call failed (see sage3_last_cuda_error)  */
+  SAGE3_ERR_DEVICE_WAIT = 4   /* a bounded wait inside a kernel gave up (read back via
+                                 sage3_read_device_status)                                        */
+};
+
+typedef struct {
+  int32_t B;      /* batch                                   */
+  int32_t Hq;     /* query heads                             */
+  int32_t Hkv;    /* key/value heads (Hq % Hkv == 0)         */
+  int32_t Nq;     /* query tokens                            */
+  int32_t Nk;     /* key/value tokens                        */
+  int32_t D;      /* head dim, 64 or 128                     */
+} sage3_shape;
+
+/* A bf16 [B,H,N,D] view: element strides of the batch, head and token dimensions. */
+typedef struct {
+  const void* ptr;
+  int64_t stride_b, stride_h, stride_n;
+} sage3_tensor;
+
+/* Byte sizes of the caller-owned buffers for one problem shape. */
+typedef struct {
+  size_t q_codes;   /* u8  [B,Hq ,Tq,128,D/2]           E2M1 pairs, element 2i in the low nibble   */
+  size_t q_sf;      /* u8  [B,Hq ,Tq,D/64,512]          E4M3 scales in 128-row tcgen05 SF atoms    */
+  size_t k_codes;   /* u8  [B,Hkv,Tk,128,D/2]                                                      */
+  size_t k_sf;      /* u8  [B,Hkv,Tk,D/64,512]                                                     */
+  size_t vt_codes;  /* u8  [B,Hkv,Tk,D,64]              V transposed per 128-token tile            */
+  size_t vt_sf;     /* u8  [B,Hkv,Tk,2,512]             scales over 16 consecutive tokens          */
+  size_t qm;        /* bf16 [B,Hq,Tq,D]  (per-block mean)  or [B,Hq,1,D] (whole-sequence mean)     */
+  size_t km;        /* bf16 [B,Hkv,D]                                                              */
+  size_t delta_s;   /* fp32 [B,Hq,Tq or 1,Tk*128]                                                  */
+  size_t scratch;   /* reduction scratch of the channel-mean kernel                               */
+  size_t status;    /* one int32 on the device                                                    */
+  size_t workspace; /* all of the above packed (256-byte aligned parts), for sage3_attention      */
+} sage3_sizes;        /* Tq = ceil(Nq/128), Tk = ceil(Nk/128)                                        */
+
+typedef struct {
+  sage3_shape shape;
+  sage3_tensor q, k, v;      /* any ptr may be NULL: that operand is skipped                        */
+  int32_t per_block_mean;    /* 1: Q minus its per-128-token mean (api.py:187-188); 0: Q minus its
+                                whole-(padded)-sequence mean (:190-191); -1: Q is not smoothed      */
+  int32_t smooth_k;          /* 1: K minus its per-channel token mean (api.py:184)                   */
+  const void* km_in;         /* optional bf16 [B,Hkv,D]: use these K means instead of computing them */
+  const float* qm_in;        /* optional fp32 [B,Hq,Tq,D]: use these Q block means (per_block_mean=1)*/
+  void *q_codes, *q_sf, *k_codes, *k_sf, *vt_codes, *vt_sf;
+  void* qm;                  /* out: Q means (needed when per_block_mean >= 0)                       */
+  void* km;                  /* out: K means (needed when smooth_k and km_in == NULL)                */
+  void* delta_s;             /* out, optional: delta_s_scale * bf16(qm . k_smoothed^T) as fp32       */
+  float delta_s_scale;
+  void* scratch;             /* >= sage3_sizes.scratch bytes, 256-byte aligned                       */
+  size_t scratch_bytes;
+} sage3_quant_args;
+
+typedef struct {
+  sage3_shape shape;
+  const void *q_codes, *q_sf, *k_codes, *k_sf, *vt_codes, *vt_sf;   /* layouts of sage3_sizes        */
+  const float* delta_s;      /* optional; must already be multiplied by sm_scale * log2(e)          */
+  int32_t delta_s_rows;      /* Tq, or 1 when one row serves all query blocks                        */
+  void* out;                 /* bf16, strides below (elements), last dim contiguous                  */
+  int64_t out_stride_b, out_stride_h, out_stride_n;
+  float* lse;                /* optional fp32 [B,Hq,Nq]: log-sum-exp (natural log) of the scores the
+                                kernel saw (after smoothing)                                         */
+  float sm_scale;
+  int32_t is_causal;         /* bottom-right aligned when Nq != Nk (fwd_mainloop.cu:926)             */
+  int32_t* device_status;    /* one int32 on the device; zeroed on the stream before the launch      */
+} sage3_attn_args;
+
+typedef struct {
+  sage3_shape shape;
+  sage3_tensor q, k, v;
+  void* out;
+  int64_t out_stride_b, out_stride_h, out_stride_n;
+  float* lse;                /* optional, see sage3_attn_args                                        */
+  void* km_out;              /* optional bf16 [B,Hkv,D]: K channel means (for an LSE correction)     */
+  float sm_scale;            /* <= 0: head_dim^-0.5                                                  */
+  int32_t is_causal;
+  int32_t per_block_mean;    /* as in sage3_quant_args                                               */
+  int32_t smooth_k;
+  void* workspace;           /* >= sage3_sizes.workspace bytes, 256-byte aligned                     */
+  size_t workspace_bytes;
+  int32_t* device_status;    /* optional device int32 (see sage3_attn_args); NULL: one inside the
+                                workspace is used and cannot be read back by the caller              */
+} sage3_fwd_args;
+
+SAGE3_API int sage3_version(void);
+SAGE3_API const char* sage3_status_string(int status);
+/* cudaError_t of the most recent failing CUDA call made by this thread inside the library. */
+SAGE3_API int sage3_last_cuda_error(void);
+
+SAGE3_API int sage3_buffer_sizes(const sage3_shape* shape, int per_block_mean, sage3_sizes* out);
+
+SAGE3_API int sage3_quant_qkv(const sage3_quant_args* args, void* stream);
+SAGE3_API int sage3_attn_fwd(const sage3_attn_args* args, void* stream);
+SAGE3_API int sage3_attention(const sage3_fwd_args* args, void* stream);
+
+/* Synchronises `stream`, copies the device status word back and maps it to a status
+ * (SAGE3_OK or SAGE3_ERR_DEVICE_WAIT); *code_out, if given, receives the raw word. */
+SAGE3_API int sage3_read_device_status(const int32_t* device_status, void* stream, int32_t* code_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SAGE3_B200_H */

@@ -1,0 +1,104 @@
+"""ctypes binding of ``libsage3_b200.so`` (C ABI declared in ``include/sage3_b200.h``).
+
+There is no fallback: if the shared library is missing the import fails with instructions to
+build it, and every call checks the returned status.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+_HERE = Path(__file__).resolve().parent
+LIB_PATH = _HERE / "libsage3_b200.so"
+
+OK, ERR_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE_WAIT = range(5)
+
+
+class Shape(C.Structure):
+    _fields_ = [("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32),
+                ("Nq", C.c_int32), ("Nk", C.c_int32), ("D", C.c_int32)]
+
+
+class Tensor(C.Structure):
+    _fields_ = [("ptr", C.c_void_p), ("stride_b", C.c_int64), ("stride_h", C.c_int64), ("stride_n", C.c_int64)]
+
+
+class Sizes(C.Structure):
+    _fields_ = [(n, C.c_size_t) for n in
+                ("q_codes", "q_sf", "k_codes", "k_sf", "vt_codes", "vt_sf", "qm", "km",
+                 "delta_s", "scratch", "status", "workspace")]
+
+
+class QuantArgs(C.Structure):
+    _fields_ = [("shape", Shape), ("q", Tensor), ("k", Tensor), ("v", Tensor),
+                ("per_block_mean", C.c_int32), ("smooth_k", C.c_int32),
+                ("km_in", C.c_void_p), ("qm_in", C.c_void_p),
+                ("q_codes", C.c_void_p), ("q_sf", C.c_void_p), ("k_codes", C.c_void_p), ("k_sf", C.c_void_p),
+                ("vt_codes", C.c_void_p), ("vt_sf", C.c_void_p),
+                ("qm", C.c_void_p), ("km", C.c_void_p), ("delta_s", C.c_void_p), ("delta_s_scale", C.c_float),
+                ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t)]
+
+
+class AttnArgs(C.Structure):
+    _fields_ = [("shape", Shape),
+                ("q_codes", C.c_void_p), ("q_sf", C.c_void_p), ("k_codes", C.c_void_p), ("k_sf", C.c_void_p),
+                ("vt_codes", C.c_void_p), ("vt_sf", C.c_void_p),
+                ("delta_s", C.c_void_p), ("delta_s_rows", C.c_int32),
+                ("out", C.c_void_p), ("out_stride_b", C.c_int64), ("out_stride_h", C.c_int64),
+                ("out_stride_n", C.c_int64),
+                ("lse", C.c_void_p), ("sm_scale", C.c_float), ("is_causal", C.c_int32),
+                ("device_status", C.c_void_p)]
+
+
+class FwdArgs(C.Structure):
+    _fields_ = [("shape", Shape), ("q", Tensor), ("k", Tensor), ("v", Tensor),
+                ("out", C.c_void_p), ("out_stride_b", C.c_int64), ("out_stride_h", C.c_int64),
+                ("out_stride_n", C.c_int64),
+                ("lse", C.c_void_p), ("km_out", C.c_void_p), ("sm_scale", C.c_float), ("is_causal", C.c_int32),
+                ("per_block_mean", C.c_int32), ("smooth_k", C.c_int32),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("device_status", C.c_void_p)]
+
+
+EXPORTS = ("sage3_version", "sage3_status_string", "sage3_last_cuda_error", "sage3_buffer_sizes",
+           "sage3_quant_qkv", "sage3_attn_fwd", "sage3_attention", "sage3_read_device_status")
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m sageattention_b200.build` "
+            "(nvcc, sm_100a).  There is no CPU or PyTorch fallback.")
+    lib = C.CDLL(str(LIB_PATH))
+    lib.sage3_version.restype = C.c_int
+    lib.sage3_status_string.restype = C.c_char_p
+    lib.sage3_status_string.argtypes = [C.c_int]
+    lib.sage3_last_cuda_error.restype = C.c_int
+    lib.sage3_buffer_sizes.argtypes = [C.POINTER(Shape), C.c_int, C.POINTER(Sizes)]
+    lib.sage3_quant_qkv.argtypes = [C.POINTER(QuantArgs), C.c_void_p]
+    lib.sage3_attn_fwd.argtypes = [C.POINTER(AttnArgs), C.c_void_p]
+    lib.sage3_attention.argtypes = [C.POINTER(FwdArgs), C.c_void_p]
+    lib.sage3_read_device_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
+    for name in EXPORTS:
+        getattr(lib, name)            # raises AttributeError if an export is missing
+    _lib = lib
+    return lib
+
+
+class Sage3Error(RuntimeError):
+    def __init__(self, status: int, where: str):
+        lib = load()
+        msg = lib.sage3_status_string(status).decode()
+        if status == ERR_CUDA:
+            msg += f" [cudaError {lib.sage3_last_cuda_error()}]"
+        super().__init__(f"{where}: {msg}")
+        self.status = status
+
+
+def check(status: int, where: str) -> None:
+    if status != OK:
+        raise Sage3Error(status, where)

@@ -1,0 +1,281 @@
+"""Python operator API of the B200 FP4 attention path.
+
+Mirrors the reference's operator interface:
+
+* ``sageattn(q, k, v, tensor_layout, is_causal, sm_scale, return_lse)`` - signature and semantics
+  of ``sageattention/core.py:79-157`` (layouts "HND" ``[B,H,N,D]`` / "NHD" ``[B,N,H,D]``, GQA with
+  ``Hq % Hkv == 0``, default scale ``D**-0.5``, optional log-sum-exp output);
+* ``sageattn3_blackwell(q, k, v, ...)`` - the FP4 operator of
+  ``sageattention3_blackwell/sageattn4/api.py:250-288`` without the fork's K-packing steps;
+* ``sageattn_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, ...)`` - ``sageattention/core.py:334-448``.
+
+All tensor work happens in ``libsage3_b200.so`` (hand-written sm_100a CUDA behind a C ABI); this
+file only allocates buffers, turns layouts into strides and passes pointers.  There is no
+fallback path: without the library, or on a GPU that is not compute capability 10.x, the calls
+raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+_LOG2E = 1.4426950408889634
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _as_bhnd_strides(x: torch.Tensor, tensor_layout: str):
+    """(B, H, N, D, stride_b, stride_h, stride_n) of a 4-D tensor in either layout."""
+    if x.dim() != 4:
+        raise ValueError("expected a 4-D tensor")
+    if x.stride(-1) != 1:
+        raise ValueError("the last dimension must be contiguous")       # core.py:274-277
+    if tensor_layout == "HND":
+        B, H, N, D = x.shape
+        return B, H, N, D, x.stride(0), x.stride(1), x.stride(2)
+    if tensor_layout == "NHD":
+        B, N, H, D = x.shape
+        return B, H, N, D, x.stride(0), x.stride(2), x.stride(1)
+    raise ValueError(f"Unknown tensor layout: {tensor_layout}")
+
+
+def _tensor_arg(x: torch.Tensor, sb, sh, sn) -> _lib.Tensor:
+    return _lib.Tensor(x.data_ptr(), sb, sh, sn)
+
+
+def _check_device(x: torch.Tensor):
+    if not x.is_cuda:
+        raise ValueError("sageattention_b200 runs on CUDA tensors only (no CPU path)")
+    major, _ = torch.cuda.get_device_capability(x.device)
+    if major != 10:
+        raise ValueError(f"unsupported GPU: compute capability {torch.cuda.get_device_capability(x.device)}; "
+                         "this build targets B200 (sm_100a) only")
+
+
+def buffer_sizes(B: int, Hq: int, Hkv: int, Nq: int, Nk: int, D: int, per_block_mean: int = 1) -> _lib.Sizes:
+    lib = _lib.load()
+    z = _lib.Sizes()
+    shape = _lib.Shape(B, Hq, Hkv, Nq, Nk, D)
+    _lib.check(lib.sage3_buffer_sizes(C.byref(shape), per_block_mean, C.byref(z)), "sage3_buffer_sizes")
+    return z
+
+
+@dataclass
+class QuantizedQKV:
+    """Device buffers produced by :func:`quantize_qkv` (layouts in ``include/sage3_b200.h``)."""
+    shape: Tuple[int, int, int, int, int, int]       # B, Hq, Hkv, Nq, Nk, D
+    q_codes: torch.Tensor
+    q_sf: torch.Tensor
+    k_codes: torch.Tensor
+    k_sf: torch.Tensor
+    vt_codes: torch.Tensor
+    vt_sf: torch.Tensor
+    qm: Optional[torch.Tensor]
+    km: Optional[torch.Tensor]
+    delta_s: Optional[torch.Tensor]
+    delta_s_rows: int
+
+
+def quantize_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",
+                 per_block_mean: Optional[bool] = True, smooth_k: bool = True, delta_s_scale: Optional[float] = 1.0,
+                 km: Optional[torch.Tensor] = None, qm_fp32: Optional[torch.Tensor] = None) -> QuantizedQKV:
+    """Smoothing + NVFP4 quantisation of Q, K, V in one fused launch.
+
+    Stands in for ``preprocess_qkv`` + ``scale_and_quant_fp4`` / ``_permute`` / ``_transpose`` of
+    ``sageattn4/api.py:112-229``.  ``per_block_mean``: True = per-128-token Q mean, False = whole
+    sequence Q mean, None = leave Q as is.  ``delta_s_scale=None`` skips delta_s.  ``km`` / ``qm_fp32``
+    let a caller supply the means (used by the parity tests to separate rounding of the means from
+    the quantiser).
+    """
+    lib = _lib.load()
+    _check_device(q)
+    for t in (q, k, v):
+        if t.dtype != torch.bfloat16:
+            raise AssertionError("TODO: support inputs other than bfloat16")     # api.py:257
+    B, Hq, Nq, D, qsb, qsh, qsn = _as_bhnd_strides(q, tensor_layout)
+    Bk, Hkv, Nk, Dk, ksb, ksh, ksn = _as_bhnd_strides(k, tensor_layout)
+    Bv, Hv, Nv, Dv, vsb, vsh, vsn = _as_bhnd_strides(v, tensor_layout)
+    if not (B == Bk == Bv and D == Dk == Dv and Hkv == Hv and Nk == Nv):
+        raise ValueError("q, k, v shapes do not match")
+    pbm = -1 if per_block_mean is None else int(bool(per_block_mean))
+    z = buffer_sizes(B, Hq, Hkv, Nq, Nk, D, pbm)
+    dev = q.device
+    u8 = dict(dtype=torch.uint8, device=dev)
+    Tq, Tk = (Nq + 127) // 128, (Nk + 127) // 128
+    out = QuantizedQKV(
+        shape=(B, Hq, Hkv, Nq, Nk, D),
+        q_codes=torch.empty((B, Hq, Tq, 128, D // 2), **u8), q_sf=torch.empty((B, Hq, Tq, D // 64, 512), **u8),
+        k_codes=torch.empty((B, Hkv, Tk, 128, D // 2), **u8), k_sf=torch.empty((B, Hkv, Tk, D // 64, 512), **u8),
+        vt_codes=torch.empty((B, Hkv, Tk, D, 64), **u8), vt_sf=torch.empty((B, Hkv, Tk, 2, 512), **u8),
+        qm=None, km=None, delta_s=None, delta_s_rows=1)
+    ds_rows = Tq if pbm == 1 else 1
+    if pbm >= 0:
+        out.qm = torch.empty((B, Hq, ds_rows, D), dtype=torch.bfloat16, device=dev)
+        if delta_s_scale is not None:
+            out.delta_s = torch.empty((B, Hq, ds_rows, Tk * 128), dtype=torch.float32, device=dev)
+            out.delta_s_rows = ds_rows
+    if smooth_k:
+        out.km = km.contiguous() if km is not None else torch.empty((B, Hkv, D), dtype=torch.bfloat16, device=dev)
+    scratch = torch.empty(max(int(z.scratch), 256), **u8)
+    a = _lib.QuantArgs()
+    a.shape = _lib.Shape(B, Hq, Hkv, Nq, Nk, D)
+    a.q, a.k, a.v = _tensor_arg(q, qsb, qsh, qsn), _tensor_arg(k, ksb, ksh, ksn), _tensor_arg(v, vsb, vsh, vsn)
+    a.per_block_mean, a.smooth_k = pbm, int(smooth_k)
+    a.km_in = out.km.data_ptr() if (smooth_k and km is not None) else None
+    if qm_fp32 is not None:
+        qm_fp32 = qm_fp32.to(device=dev, dtype=torch.float32).contiguous()
+        a.qm_in = qm_fp32.data_ptr()
+    a.q_codes, a.q_sf = out.q_codes.data_ptr(), out.q_sf.data_ptr()
+    a.k_codes, a.k_sf = out.k_codes.data_ptr(), out.k_sf.data_ptr()
+    a.vt_codes, a.vt_sf = out.vt_codes.data_ptr(), out.vt_sf.data_ptr()
+    a.qm = out.qm.data_ptr() if out.qm is not None else None
+    a.km = out.km.data_ptr() if out.km is not None else None
+    a.delta_s = out.delta_s.data_ptr() if out.delta_s is not None else None
+    a.delta_s_scale = float(delta_s_scale) if delta_s_scale is not None else 1.0
+    a.scratch, a.scratch_bytes = scratch.data_ptr(), scratch.numel()
+    with torch.cuda.device(dev):
+        _lib.check(lib.sage3_quant_qkv(C.byref(a), _stream_ptr(dev)), "sage3_quant_qkv")
+    return out
+
+
+def fp4_attention(qz: QuantizedQKV, sm_scale: Optional[float] = None, is_causal: bool = False,
+                  tensor_layout: str = "HND", return_lse: bool = False, check_status: bool = False):
+    """Attention on quantised operands (``blockscaled_fp4_attn``, ``sageattn4/api.py:231-243`` ->
+    ``mha_fwd``, ``blackwell/api.cpp:258``).  ``qz.delta_s`` must have been produced with
+    ``delta_s_scale = sm_scale * log2(e)``."""
+    lib = _lib.load()
+    B, Hq, Hkv, Nq, Nk, D = qz.shape
+    dev = qz.q_codes.device
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    if tensor_layout == "HND":
+        out = torch.empty((B, Hq, Nq, D), dtype=torch.bfloat16, device=dev)
+        osb, osh, osn = out.stride(0), out.stride(1), out.stride(2)
+    else:
+        out = torch.empty((B, Nq, Hq, D), dtype=torch.bfloat16, device=dev)
+        osb, osh, osn = out.stride(0), out.stride(2), out.stride(1)
+    lse = torch.empty((B, Hq, Nq), dtype=torch.float32, device=dev) if return_lse else None
+    status = torch.empty(1, dtype=torch.int32, device=dev)
+    a = _lib.AttnArgs()
+    a.shape = _lib.Shape(B, Hq, Hkv, Nq, Nk, D)
+    a.q_codes, a.q_sf = qz.q_codes.data_ptr(), qz.q_sf.data_ptr()
+    a.k_codes, a.k_sf = qz.k_codes.data_ptr(), qz.k_sf.data_ptr()
+    a.vt_codes, a.vt_sf = qz.vt_codes.data_ptr(), qz.vt_sf.data_ptr()
+    a.delta_s = qz.delta_s.data_ptr() if qz.delta_s is not None else None
+    a.delta_s_rows = qz.delta_s_rows
+    a.out, a.out_stride_b, a.out_stride_h, a.out_stride_n = out.data_ptr(), osb, osh, osn
+    a.lse = lse.data_ptr() if lse is not None else None
+    a.sm_scale, a.is_causal = float(sm_scale), int(bool(is_causal))
+    a.device_status = status.data_ptr()
+    with torch.cuda.device(dev):
+        _lib.check(lib.sage3_attn_fwd(C.byref(a), _stream_ptr(dev)), "sage3_attn_fwd")
+        if check_status:
+            _lib.check(lib.sage3_read_device_status(status.data_ptr(), _stream_ptr(dev), None), "attention kernel")
+    return (out, lse) if return_lse else out
+
+
+def sageattn3_blackwell(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",
+                        is_causal: bool = False, sm_scale: Optional[float] = None, per_block_mean: bool = True,
+                        return_lse: bool = False, smooth_k: bool = True, attn_mask=None,
+                        check_status: bool = False, **kwargs):
+    """FP4 attention, drop-in for ``sageattn4_blackwell`` (``sageattn4/api.py:250-288``) with the wider
+    argument set of ``sageattn`` (``sageattention/core.py:79-88``).
+
+    q ``[B,Hq,Nq,D]`` ("HND") or ``[B,Nq,Hq,D]`` ("NHD"), k/v likewise with ``Hkv`` heads
+    (``Hq % Hkv == 0``), bf16, D in {64, 128}.  Returns a tensor shaped like q (and the natural-log
+    LSE ``[B,Hq,Nq]`` when ``return_lse``).  Causal masking is bottom-right aligned when Nq != Nk.
+    """
+    if attn_mask is not None:
+        raise NotImplementedError("attn_mask is not supported (the reference ignores it as well)")
+    lib = _lib.load()
+    _check_device(q)
+    for t in (q, k, v):
+        if t.dtype != torch.bfloat16:
+            raise AssertionError("TODO: support inputs other than bfloat16")     # api.py:257
+    B, Hq, Nq, D, qsb, qsh, qsn = _as_bhnd_strides(q, tensor_layout)
+    Bk, Hkv, Nk, Dk, ksb, ksh, ksn = _as_bhnd_strides(k, tensor_layout)
+    Bv, Hv, Nv, Dv, vsb, vsh, vsn = _as_bhnd_strides(v, tensor_layout)
+    if not (B == Bk == Bv and D == Dk == Dv and Hkv == Hv and Nk == Nv):
+        raise ValueError("q, k, v shapes do not match")
+    if D not in (64, 128):
+        raise ValueError(f"Unsupported Headdim {D}")                              # api.py:253-255
+    if Hq % Hkv != 0:
+        raise ValueError("num_qo_heads must be a multiple of num_kv_heads")
+    dev = q.device
+    pbm = int(bool(per_block_mean))
+    z = buffer_sizes(B, Hq, Hkv, Nq, Nk, D, pbm)
+    out = torch.empty_like(q)
+    _, _, _, _, osb, osh, osn = _as_bhnd_strides(out, tensor_layout)
+    ws = torch.empty(int(z.workspace), dtype=torch.uint8, device=dev)
+    lse = torch.empty((B, Hq, Nq), dtype=torch.float32, device=dev) if return_lse else None
+    km = torch.empty((B, Hkv, D), dtype=torch.bfloat16, device=dev) if (return_lse and smooth_k) else None
+    status = torch.empty(1, dtype=torch.int32, device=dev)
+    a = _lib.FwdArgs()
+    a.shape = _lib.Shape(B, Hq, Hkv, Nq, Nk, D)
+    a.q, a.k, a.v = _tensor_arg(q, qsb, qsh, qsn), _tensor_arg(k, ksb, ksh, ksn), _tensor_arg(v, vsb, vsh, vsn)
+    a.out, a.out_stride_b, a.out_stride_h, a.out_stride_n = out.data_ptr(), osb, osh, osn
+    a.lse = lse.data_ptr() if lse is not None else None
+    a.km_out = km.data_ptr() if km is not None else None
+    a.sm_scale = float(sm_scale) if sm_scale is not None else 0.0
+    a.is_causal, a.per_block_mean, a.smooth_k = int(bool(is_causal)), pbm, int(bool(smooth_k))
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    a.device_status = status.data_ptr()
+    with torch.cuda.device(dev):
+        _lib.check(lib.sage3_attention(C.byref(a), _stream_ptr(dev)), "sage3_attention")
+        if check_status:
+            _lib.check(lib.sage3_read_device_status(status.data_ptr(), _stream_ptr(dev), None), "attention kernel")
+    if not return_lse:
+        return out
+    if km is not None:
+        # the kernel saw scores q.(k - km); put the removed term back (core.py:993-994 pattern)
+        scale = float(sm_scale) if sm_scale is not None else D ** -0.5
+        qf = q.float() if tensor_layout == "HND" else q.float().transpose(1, 2)
+        kmf = km.float().repeat_interleave(Hq // Hkv, dim=1)
+        lse = lse + scale * torch.einsum("bhnd,bhd->bhn", qf, kmf)
+    return out, lse
+
+
+def sageattn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND", is_causal: bool = False,
+             sm_scale: Optional[float] = None, return_lse: bool = False, **kwargs):
+    """Automatic entry point (``sageattention/core.py:79-157``).  The reference picks a kernel family
+    by GPU architecture and raises ``ValueError`` for architectures it has no kernel for; this build
+    has exactly one family, the FP4 kernels for compute capability 10.x."""
+    _check_device(q)
+    return sageattn3_blackwell(q, k, v, tensor_layout=tensor_layout, is_causal=is_causal, sm_scale=sm_scale,
+                               return_lse=return_lse, **kwargs)
+
+
+def sageattn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q: torch.Tensor,
+                    cu_seqlens_k: torch.Tensor, max_seqlen_q: int, max_seqlen_k: int, is_causal: bool = False,
+                    sm_scale: Optional[float] = None, smooth_k: bool = True, **kwargs) -> torch.Tensor:
+    """Variable-length batch (``sageattention/core.py:334-448``): q ``[sum(len_q), Hq, D]``, k/v
+    ``[sum(len_k), Hkv, D]``, ``cu_seqlens_*`` the int32 prefix sums (length batch + 1).  Each sequence
+    is smoothed, quantised and attended on its own (K means never mix sequences)."""
+    if q.dim() != 3 or k.dim() != 3 or v.dim() != 3:
+        raise ValueError("varlen tensors must be [tokens, heads, head_dim]")
+    cq = cu_seqlens_q.tolist()
+    ck = cu_seqlens_k.tolist()
+    if len(cq) != len(ck) or cq[0] != 0 or ck[0] != 0:
+        raise ValueError("cu_seqlens_q and cu_seqlens_k must both start at 0 and have batch + 1 entries")
+    out = torch.empty_like(q)
+    for i in range(len(cq) - 1):
+        lq, lk = cq[i + 1] - cq[i], ck[i + 1] - ck[i]
+        if lq > max_seqlen_q or lk > max_seqlen_k:
+            raise ValueError("sequence longer than max_seqlen")
+        if lq == 0:
+            continue
+        if lk == 0:
+            out[cq[i]:cq[i + 1]].zero_()
+            continue
+        oi = sageattn3_blackwell(q[cq[i]:cq[i + 1]].unsqueeze(0), k[ck[i]:ck[i + 1]].unsqueeze(0),
+                                 v[ck[i]:ck[i + 1]].unsqueeze(0), tensor_layout="NHD", is_causal=is_causal,
+                                 sm_scale=sm_scale, smooth_k=smooth_k, **kwargs)
+        out[cq[i]:cq[i + 1]] = oi[0]
+    return out

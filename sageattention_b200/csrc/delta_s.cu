@@ -1,0 +1,113 @@
+// delta_s[b, hq, qb, n] = out_scale * bf16( sum_d qm[b, hq, qb, d] * ks[b, hkv, n, d] ),  ks = bf16(k - km)
+//
+// Replaces `delta_s = torch.matmul(qm, k.transpose(-2, -1)).to(torch.float32)` of
+// sageattn4/api.py:201: a bf16 GEMM (fp32 accumulation, bf16 result) widened to fp32.  The
+// attention kernel adds row qb of delta_s to every score of query block qb, which restores the Q
+// block mean that was removed before quantisation; out_scale lets the caller fold the softmax
+// scale (sm_scale * log2 e) in so that the kernel needs one fused multiply-add per score.
+//
+// One CTA per (128-key tile, kv head): the smoothed K tile is rebuilt in shared memory once and
+// multiplied against the block means of every query head of the GQA group.  The fp32 output
+// ([Tq x 128] per CTA and head) dominates the traffic, so the small contraction runs on
+// mma.sync m16n8k16 with fragments read straight from shared memory, and every quad of lanes
+// stores one full 32-byte sector.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace sage3 {
+
+template <int D>
+__global__ void __launch_bounds__(256) delta_s_kernel(
+    const __nv_bfloat16* __restrict__ qm, const __nv_bfloat16* __restrict__ k, int64_t k_sb, int64_t k_sh,
+    int64_t k_sn, const __nv_bfloat16* __restrict__ km, float* __restrict__ ds, int Hq, int Hkv, int Tq,
+    int Nk, int Nk_pad, float out_scale) {
+  constexpr int PITCH = D + 8;                         // bf16 elements; 4-bank skew per row
+  extern __shared__ __align__(16) unsigned char dyn_smem[];
+  __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(dyn_smem);              // [128][PITCH]
+  const int tile = blockIdx.x, bh = blockIdx.y, b = bh / Hkv, hkv = bh % Hkv, G = Hq / Hkv;
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31, g = lane >> 2, tg = lane & 3;
+
+  {  // smoothed K tile -> shared
+    constexpr int CH = D / 8, RPP = 256 / CH;
+    const int c = t % CH, rl = t / CH;
+    float mean[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (km != nullptr) {
+      uint4 m = *reinterpret_cast<const uint4*>(km + (int64_t)bh * D + c * 8);
+      mean[0] = bf16_lo(m.x); mean[1] = bf16_hi(m.x); mean[2] = bf16_lo(m.y); mean[3] = bf16_hi(m.y);
+      mean[4] = bf16_lo(m.z); mean[5] = bf16_hi(m.z); mean[6] = bf16_lo(m.w); mean[7] = bf16_hi(m.w);
+    }
+    const __nv_bfloat16* src = k + b * k_sb + hkv * k_sh + c * 8;
+#pragma unroll
+    for (int p = 0; p < 128 / RPP; ++p) {
+      const int r = p * RPP + rl, n = tile * 128 + r;
+      uint4 w = make_uint4(0, 0, 0, 0);
+      if (n < Nk) {
+        w = *reinterpret_cast<const uint4*>(src + (int64_t)n * k_sn);
+        w.x = pack_bf16(bf16_lo(w.x) - mean[0], bf16_hi(w.x) - mean[1]);
+        w.y = pack_bf16(bf16_lo(w.y) - mean[2], bf16_hi(w.y) - mean[3]);
+        w.z = pack_bf16(bf16_lo(w.z) - mean[4], bf16_hi(w.z) - mean[5]);
+        w.w = pack_bf16(bf16_lo(w.w) - mean[6], bf16_hi(w.w) - mean[7]);
+      }
+      *reinterpret_cast<uint4*>(&ks[r * PITCH + c * 8]) = w;
+    }
+  }
+  __syncthreads();
+
+  const int M = G * Tq;
+  const uint32_t* ks32 = reinterpret_cast<const uint32_t*>(ks);
+  for (int m0 = warp * 16; m0 < M; m0 += 8 * 16) {
+    // A fragments: rows m0+g and m0+g+8 of the stacked block means of this GQA group
+    uint32_t a[D / 16][4];
+    const int r0 = m0 + g, r1 = m0 + g + 8;
+    const uint32_t* p0 = nullptr; const uint32_t* p1 = nullptr;
+    if (r0 < M) p0 = reinterpret_cast<const uint32_t*>(qm + (((int64_t)b * Hq + hkv * G + r0 / Tq) * Tq + r0 % Tq) * D);
+    if (r1 < M) p1 = reinterpret_cast<const uint32_t*>(qm + (((int64_t)b * Hq + hkv * G + r1 / Tq) * Tq + r1 % Tq) * D);
+#pragma unroll
+    for (int s = 0; s < D / 16; ++s) {
+      a[s][0] = p0 ? p0[s * 8 + tg] : 0u;
+      a[s][1] = p1 ? p1[s * 8 + tg] : 0u;
+      a[s][2] = p0 ? p0[s * 8 + 4 + tg] : 0u;
+      a[s][3] = p1 ? p1[s * 8 + 4 + tg] : 0u;
+    }
+    float* d0 = r0 < M ? ds + ((((int64_t)b * Hq + hkv * G + r0 / Tq) * Tq + r0 % Tq) * Nk_pad + tile * 128) : nullptr;
+    float* d1 = r1 < M ? ds + ((((int64_t)b * Hq + hkv * G + r1 / Tq) * Tq + r1 % Tq) * Nk_pad + tile * 128) : nullptr;
+#pragma unroll 4
+    for (int nt = 0; nt < 16; ++nt) {
+      float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
+      const uint32_t* brow = ks32 + (nt * 8 + g) * (PITCH / 2) + tg;
+#pragma unroll
+      for (int s = 0; s < D / 16; ++s) {
+        uint32_t b0 = brow[s * 8], b1 = brow[s * 8 + 4];
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(c0), "+f"(c1), "+f"(c2), "+f"(c3)
+            : "r"(a[s][0]), "r"(a[s][1]), "r"(a[s][2]), "r"(a[s][3]), "r"(b0), "r"(b1));
+      }
+      // round to bf16 (the reference GEMM's output type), then widen and pre-scale.
+      // Four lanes of a quad write one full 32-byte sector per row.
+      uint32_t p01 = pack_bf16(c0, c1), p23 = pack_bf16(c2, c3);
+      if (d0) *reinterpret_cast<float2*>(d0 + nt * 8 + tg * 2) = make_float2(bf16_lo(p01) * out_scale, bf16_hi(p01) * out_scale);
+      if (d1) *reinterpret_cast<float2*>(d1 + nt * 8 + tg * 2) = make_float2(bf16_lo(p23) * out_scale, bf16_hi(p23) * out_scale);
+    }
+  }
+}
+
+cudaError_t launch_delta_s(const DeltaSArgs& a, cudaStream_t stream) {
+  const int Tk = (a.Nk + 127) / 128;
+  dim3 grid(Tk, a.B * a.Hkv);
+  const int smem = 128 * (a.D + 8) * 2;
+  // per device and cheap, so set on every call rather than cached per process
+  cudaFuncSetAttribute(delta_s_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 136 * 2);
+  cudaFuncSetAttribute(delta_s_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 72 * 2);
+  if (a.D == 128)
+    delta_s_kernel<128><<<grid, 256, smem, stream>>>((const __nv_bfloat16*)a.qm, (const __nv_bfloat16*)a.k, a.k_sb, a.k_sh,
+                                                  a.k_sn, (const __nv_bfloat16*)a.km, (float*)a.ds, a.Hq, a.Hkv,
+                                                  a.Tq, a.Nk, Tk * 128, a.out_scale);
+  else
+    delta_s_kernel<64><<<grid, 256, smem, stream>>>((const __nv_bfloat16*)a.qm, (const __nv_bfloat16*)a.k, a.k_sb, a.k_sh,
+                                                 a.k_sn, (const __nv_bfloat16*)a.km, (float*)a.ds, a.Hq, a.Hkv,
+                                                 a.Tq, a.Nk, Tk * 128, a.out_scale);
+  return cudaGetLastError();
+}
+
+}  // namespace sage3

@@ -1,0 +1,50 @@
+// Internal launch interfaces between the C-ABI layer (cabi.cu) and the kernel files.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace sage3 {
+
+struct QuantArgs {
+  const void *q, *k, *v;                  // bf16, last dim contiguous; any of them may be null (skipped)
+  int64_t q_sb, q_sh, q_sn, k_sb, k_sh, k_sn, v_sb, v_sh, v_sn;   // element strides
+  int B, Hq, Hkv, Nq, Nk, D;
+  int q_mean_mode;                        // 0 none, 1 per 128-token block, 2 whole sequence
+  const void* km;                         // bf16 [B,Hkv,D] or null (no K smoothing)
+  const void* q_mean_seq;                 // bf16 [B,Hq,D]   (mode 2)
+  const void* qm_override;                // fp32 [B,Hq,Tq,D] or null (mode 1)
+  void *q_codes, *q_sf, *k_codes, *k_sf, *vt_codes, *vt_sf, *qm;
+};
+
+size_t quant_scratch_bytes(int B, int H, int N, int D);
+cudaError_t launch_channel_mean(const void* x, int64_t sb, int64_t sh, int64_t sn, int B, int H, int N, int D,
+                                float divisor, void* scratch, void* mean_out, cudaStream_t stream);
+cudaError_t launch_quant_qkv(const QuantArgs& a, cudaStream_t stream);
+
+struct DeltaSArgs {
+  const void* qm;                         // bf16 [B,Hq,Tq,D]
+  const void* k;                          // bf16 raw K, strides below
+  int64_t k_sb, k_sh, k_sn;
+  const void* km;                         // bf16 [B,Hkv,D] or null
+  void* ds;                               // fp32 [B,Hq,Tq,Nk_pad]
+  int B, Hq, Hkv, Tq, Nk, D;
+  float out_scale;                        // multiplies the bf16-rounded dot products
+};
+cudaError_t launch_delta_s(const DeltaSArgs& a, cudaStream_t stream);
+
+struct AttnArgs {
+  const void *q_codes, *q_sf, *k_codes, *k_sf, *vt_codes, *vt_sf;
+  const void* ds;                         // fp32 [B,Hq,ds_rows,Nk_pad], already times sm_scale*log2(e); or null
+  int ds_rows;                            // Tq, or 1 when one row serves every query block
+  void* out;                              // bf16, strides below
+  int64_t o_sb, o_sh, o_sn;
+  float* lse;                             // fp32 [B,Hq,Nq] or null
+  int* status;                            // device int, set non-zero if a bounded wait gave up
+  int B, Hq, Hkv, Nq, Nk, D;
+  float sm_scale;
+  int causal;
+};
+cudaError_t launch_attn_fwd(const AttnArgs& a, cudaStream_t stream);
+
+}  // namespace sage3

@@ -1,0 +1,85 @@
+"""Generate golden vectors from the reference's own Python code (run in a container that has the
+reference checkout; the output ``.npz`` files are committed, the checkout is not needed later).
+
+    python tests/golden/make_golden.py [/path/to/reference]
+
+``sageattn4/api.py`` cannot be imported as a module (it imports two compiled CUDA extensions at the
+top), so the pure-PyTorch functions are lifted out of its syntax tree and executed unchanged:
+``round_to_blockscaled_fp4`` / ``round_to_token_blockscaled_fp4`` (api.py:77-110).
+Outputs:
+
+* ``quant_emulation.npz``  - seeded inputs (bf16 bit patterns) incl. every E2M1 tie point, and the
+  reference emulation's de-quantised result for row-wise and token-wise (transposed V) blocks.
+* ``llama_fixture_qkv.npz`` - the reference's real-activation test inputs
+  (``tests/fixtures/llama3p1_8b_instruct_l16_h30_s256_qkv.pt`` and ``..._h15_s128_qkv.pt``; inputs
+  only, the reference commits no expected outputs) as bf16 bit patterns, plus the reference
+  emulation applied to the smoothed K and to V, and the fp32 SDPA result that the reference's
+  only test compares against (tests/test.py:27-47).
+"""
+import ast
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+
+
+def lift(api_path: Path, names):
+    tree = ast.parse(api_path.read_text())
+    body = [n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name in names]
+    mod = ast.Module(body=body, type_ignores=[])
+    ns = {"torch": torch}
+    exec(compile(mod, str(api_path), "exec"), ns)
+    return [ns[n] for n in names]
+
+
+def bits(x: torch.Tensor) -> np.ndarray:
+    return x.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def main(ref_root: str):
+    ref = Path(ref_root) / "sageattention3_blackwell"
+    rtb, rttb = lift(ref / "sageattn4" / "api.py",
+                     ["round_to_blockscaled_fp4", "round_to_token_blockscaled_fp4"])
+
+    g = torch.Generator().manual_seed(0)
+    rows = [torch.zeros(16)]
+    # (1) every E2M1 midpoint, at several block scales, both signs
+    ties = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 0.0, 6.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 5.5])
+    for s in [1.0, 0.5, 2.0, 0.375, 1.75, 448.0 / 64, 2.0 ** -6, 2.0 ** -9]:
+        rows.append(ties * s)
+        rows.append(-(ties * s))
+    # (2) random normal, heavy-tailed and tiny/huge magnitude rows
+    rows += list(torch.randn(64, 16, generator=g))
+    rows += list(torch.randn(32, 16, generator=g) * torch.randn(32, 1, generator=g).exp() * 4)
+    rows += list(torch.randn(16, 16, generator=g) * 1e-3)
+    rows += list(torch.randn(16, 16, generator=g) * 300)
+    x = torch.stack(rows).to(torch.bfloat16)
+    x = x.reshape(-1, 128) if x.numel() % 128 == 0 else x[: (x.shape[0] // 8) * 8].reshape(-1, 128)
+    y = rtb(x)
+    # token-wise: [tokens=32, channels=24] blocks along tokens
+    xt = (torch.randn(2, 3, 32, 24, generator=g) * 3).to(torch.bfloat16)
+    yt = rttb(xt)
+    np.savez_compressed(HERE / "quant_emulation.npz", x=bits(x), y=bits(y), xt=bits(xt), yt=bits(yt))
+    print("quant_emulation.npz", x.shape, xt.shape)
+
+    out = {}
+    for tag, name in [("s256", "llama3p1_8b_instruct_l16_h30_s256_qkv.pt"),
+                      ("s128", "llama3p1_8b_instruct_l16_h15_s128_qkv.pt")]:
+        d = torch.load(ref / "tests" / "fixtures" / name, map_location="cpu")
+        q, k, v = d["q"], d["k"], d["v"]
+        ks = k - k.mean(dim=-2, keepdim=True)                      # api.py:184
+        out[f"{tag}_q"], out[f"{tag}_k"], out[f"{tag}_v"] = bits(q), bits(k), bits(v)
+        out[f"{tag}_ks"] = bits(ks)
+        out[f"{tag}_ks_fq"] = bits(rtb(ks))
+        out[f"{tag}_v_fq"] = bits(rttb(v))
+        sd = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float())
+        out[f"{tag}_sdpa"] = sd.numpy()
+    np.savez_compressed(HERE / "llama_fixture_qkv.npz", **out)
+    print("llama_fixture_qkv.npz", {k_: v_.shape for k_, v_ in out.items()})
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

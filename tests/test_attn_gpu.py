@@ -1,0 +1,168 @@
+"""GPU parity of the FP4 attention kernel and of the whole operator.
+
+Tolerance (floating point): cosine similarity >= 0.999 and relative L1 <= 2e-2 against the CPU
+restatement of the reference arithmetic (oracle/sage3.py); both numbers are also checked, with the
+reference test's own thresholds (tests/test.py:36-47: 1 - cos < 0.01), against fp32 SDPA.
+"""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import sageattention_b200 as sa
+from oracle import nvfp4, sage3
+from tests import _util as U
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+COS_MIN, REL_L1_MAX = 0.999, 2e-2
+LOG2E = 1.4426950408889634
+
+
+def oracle_on_device_operands(z, sm_scale, causal, return_lse=False):
+    """CPU oracle fed with the very codes / scales / delta_s the GPU kernel consumes."""
+    B, Hq, Hkv, Nq, Nk, D = z.shape
+    qc, qs = U.unpack_rows(z.q_codes, z.q_sf)
+    kc, ks = U.unpack_rows(z.k_codes, z.k_sf)
+    vc, vs = U.unpack_vt(z.vt_codes, z.vt_sf)
+    qd = torch.from_numpy(nvfp4.dequantize_nvfp4(qc, qs))
+    kd = torch.from_numpy(nvfp4.dequantize_nvfp4(kc, ks))
+    vtd = torch.from_numpy(nvfp4.dequantize_nvfp4(vc, vs))
+    ds = None
+    if z.delta_s is not None:
+        ds = z.delta_s.cpu() / (sm_scale * LOG2E)
+        if z.delta_s_rows == 1:
+            ds = ds.expand(-1, -1, qd.shape[2] // 128, -1)
+    return sage3.attention_quantised(qd, kd, vtd, ds, Nq, Nk, sm_scale, causal, return_lse)
+
+
+CASES = [
+    # B, Hq, Hkv, Nq, Nk, D, causal
+    (1, 2, 2, 128, 128, 128, False),
+    (1, 2, 2, 256, 256, 128, False),
+    (1, 8, 8, 1024, 1024, 128, False),      # benchmark config 1 shape
+    (2, 4, 4, 512, 512, 128, True),
+    (1, 8, 2, 640, 640, 128, True),         # GQA
+    (1, 2, 2, 200, 333, 128, False),        # ragged, Nq != Nk
+    (1, 2, 2, 333, 200, 128, True),         # causal with more queries than keys (rows without keys)
+    (1, 2, 1, 200, 333, 128, True),
+    (1, 4, 4, 512, 512, 64, False),
+    (1, 4, 2, 300, 300, 64, True),
+    (1, 1, 1, 1, 1, 128, False),
+    (1, 1, 1, 17, 5, 64, False),
+]
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Nq,Nk,D,causal", CASES)
+def test_kernel_matches_oracle_on_same_operands(B, Hq, Hkv, Nq, Nk, D, causal):
+    q, k, v = U.make_qkv(B, Hq, Hkv, Nq, Nk, D, seed=Nq + Nk + D, device=DEV)
+    sm_scale = D ** -0.5
+    z = sa.quantize_qkv(q, k, v, delta_s_scale=sm_scale * LOG2E)
+    out, lse = sa.fp4_attention(z, sm_scale=sm_scale, is_causal=causal, return_lse=True, check_status=True)
+    want, want_lse = oracle_on_device_operands(z, sm_scale, causal, return_lse=True)
+    assert torch.isfinite(out).all()
+    cos, l1 = sage3.accuracy(out.float().cpu(), want.to(torch.bfloat16).float())
+    assert cos >= COS_MIN and l1 <= REL_L1_MAX, (cos, l1)
+    fin = torch.isfinite(want_lse)
+    assert torch.allclose(lse.cpu()[fin], want_lse[fin], atol=2e-3, rtol=1e-4)
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Nq,Nk,D,causal", CASES[:10])
+@pytest.mark.parametrize("layout", ["HND", "NHD"])
+def test_operator_matches_emulation_and_sdpa(B, Hq, Hkv, Nq, Nk, D, causal, layout):
+    q, k, v = U.make_qkv(B, Hq, Hkv, Nq, Nk, D, seed=7 + Nq, k_offset_std=2.0, layout=layout, device=DEV)
+    out = sa.sageattn(q, k, v, tensor_layout=layout, is_causal=causal, check_status=True)
+    assert out.shape == q.shape and out.dtype == torch.bfloat16
+    qh, kh, vh = (t.cpu() if layout == "HND" else t.cpu().transpose(1, 2) for t in (q, k, v))
+    oh = out.cpu() if layout == "HND" else out.cpu().transpose(1, 2)
+    mode = "device" if nvfp4.device_tables() is not None else "exact"
+    emu = sage3.sageattn3_emulated(qh, kh, vh, is_causal=causal, mode=mode)
+    cos, l1 = sage3.accuracy(oh.float(), emu.float())
+    assert cos >= COS_MIN and l1 <= REL_L1_MAX, ("vs emulation", cos, l1)
+    ref = sage3.sdpa_fp32(qh, kh, vh, is_causal=causal)
+    cos2, l12 = sage3.accuracy(oh.float(), ref)
+    assert 1 - cos2 < 0.01, ("vs sdpa", cos2, l12)
+
+
+def test_sm_scale_and_lse_against_sdpa():
+    B, H, N, D = 1, 4, 384, 128
+    q, k, v = U.make_qkv(B, H, H, N, N, D, seed=21, device=DEV)
+    sm = 0.05
+    out, lse = sa.sageattn3_blackwell(q, k, v, sm_scale=sm, return_lse=True, check_status=True)
+    s = torch.matmul(q.float().cpu(), k.float().cpu().transpose(-2, -1)) * sm
+    want_lse = torch.logsumexp(s, dim=-1)
+    assert (lse.cpu() - want_lse).abs().max() < 0.05
+    ref = sage3.sdpa_fp32(q.cpu(), k.cpu(), v.cpu(), sm_scale=sm)
+    cos, _ = sage3.accuracy(out.float().cpu(), ref)
+    assert 1 - cos < 0.01
+
+
+def test_whole_sequence_mean_and_no_smoothing_variants():
+    q, k, v = U.make_qkv(1, 2, 2, 384, 384, 128, seed=4, device=DEV)
+    ref = sage3.sdpa_fp32(q.cpu(), k.cpu(), v.cpu())
+    for kw in (dict(per_block_mean=False), dict(smooth_k=False)):
+        out = sa.sageattn3_blackwell(q, k, v, check_status=True, **kw)
+        cos, _ = sage3.accuracy(out.float().cpu(), ref)
+        assert 1 - cos < 0.02, (kw, cos)
+    emu = sage3.sageattn3_emulated(q.cpu(), k.cpu(), v.cpu(), per_block_mean=False)
+    out = sa.sageattn3_blackwell(q, k, v, per_block_mean=False, check_status=True)
+    cos, l1 = sage3.accuracy(out.float().cpu(), emu.float())
+    assert cos >= COS_MIN and l1 <= REL_L1_MAX
+
+
+@pytest.mark.parametrize("tag", ["s128", "s256"])
+def test_reference_llama_fixtures(tag):
+    # the reference's only test (tests/test.py): real activations, thresholds vs SDPA
+    z = np.load(Path(__file__).parent / "golden" / "llama_fixture_qkv.npz")
+    q, k, v = (torch.from_numpy(nvfp4.from_bf16_bits(z[f"{tag}_{n}"])).to(torch.bfloat16).to(DEV) for n in "qkv")
+    out = sa.sageattn3_blackwell(q, k, v, is_causal=False, per_block_mean=True, check_status=True).float().cpu()
+    ref = torch.from_numpy(z[f"{tag}_sdpa"])
+    cos = torch.nn.functional.cosine_similarity(out, ref, dim=-1).mean().item()
+    l1 = torch.nn.functional.l1_loss(out, ref).item()
+    assert 1 - cos < 0.01 and l1 < 0.01, (cos, l1)
+
+
+def test_varlen_matches_per_sequence_calls():
+    Hq, Hkv, D = 4, 2, 128
+    lens_q, lens_k = [100, 257, 1, 64], [130, 257, 40, 64]
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(sum(lens_q), Hq, D, generator=g).to(torch.bfloat16).to(DEV)
+    k = (torch.randn(sum(lens_k), Hkv, D, generator=g) + 1.5).to(torch.bfloat16).to(DEV)
+    v = torch.randn(sum(lens_k), Hkv, D, generator=g).to(torch.bfloat16).to(DEV)
+    cq = torch.tensor([0] + np.cumsum(lens_q).tolist(), dtype=torch.int32, device=DEV)
+    ck = torch.tensor([0] + np.cumsum(lens_k).tolist(), dtype=torch.int32, device=DEV)
+    out = sa.sageattn_varlen(q, k, v, cq, ck, max(lens_q), max(lens_k), is_causal=True)
+    assert out.shape == q.shape
+    for i in range(len(lens_q)):
+        qs, ks = slice(int(cq[i]), int(cq[i + 1])), slice(int(ck[i]), int(ck[i + 1]))
+        ref = sage3.sdpa_fp32(q[qs].cpu().transpose(0, 1)[None], k[ks].cpu().transpose(0, 1)[None],
+                              v[ks].cpu().transpose(0, 1)[None], is_causal=True)[0].transpose(0, 1)
+        cos, _ = sage3.accuracy(out[qs].float().cpu(), ref)
+        assert 1 - cos < 0.02, (i, cos)
+
+
+def test_full_size_properties():
+    """Size-independent checks at a benchmark-sized problem (too large for the CPU oracle):
+    (1) rows of V all equal -> output equals that row; (2) permuting the keys (and values) leaves the
+    output unchanged up to quantisation noise; (3) attention over keys [A | B] equals the LSE-weighted
+    merge of attention over A and over B."""
+    B, H, N, D = 1, 4, 8192, 128
+    q, k, v = U.make_qkv(B, H, H, N, N, D, seed=99, device=DEV)
+    vc = v[:, :, :1].expand(-1, -1, N, -1).contiguous()
+    out = sa.sageattn3_blackwell(q, k, vc, check_status=True)
+    cos, l1 = sage3.accuracy(out.float().cpu(), vc.float().cpu())
+    assert cos > 0.999 and l1 < 2e-2, (cos, l1)
+    base, lse = sa.sageattn3_blackwell(q, k, v, return_lse=True, check_status=True)
+    perm = torch.randperm(N, device=DEV)
+    outp = sa.sageattn3_blackwell(q, k[:, :, perm].contiguous(), v[:, :, perm].contiguous(), check_status=True)
+    cos, l1 = sage3.accuracy(outp.float().cpu(), base.float().cpu())
+    assert cos > 0.995, (cos, l1)
+    h = N // 2
+    oa, la = sa.sageattn3_blackwell(q, k[:, :, :h].contiguous(), v[:, :, :h].contiguous(), return_lse=True)
+    ob, lb = sa.sageattn3_blackwell(q, k[:, :, h:].contiguous(), v[:, :, h:].contiguous(), return_lse=True)
+    lm = torch.logaddexp(la, lb)
+    merged = oa.float() * (la - lm).exp()[..., None] + ob.float() * (lb - lm).exp()[..., None]
+    cos, l1 = sage3.accuracy(merged.cpu(), base.float().cpu())
+    assert cos > 0.995, (cos, l1)
+    assert (lm - lse).abs().max() < 0.05
