@@ -175,14 +175,14 @@ def attention_quantised(qd: torch.Tensor, kd: torch.Tensor, vtd: torch.Tensor, d
 
 def sageattn3_emulated(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool = False,
                        sm_scale: float | None = None, per_block_mean: bool = True,
-                       mode: str = "exact", return_lse: bool = False):
+                       mode: str = "exact", return_lse: bool = False, smooth: bool = True):
     """Whole pipeline on HND bf16 CPU tensors (GQA allowed: Hq multiple of Hk)."""
     D = q.shape[-1]
     Lq, Lk = q.shape[-2], k.shape[-2]
     if sm_scale is None:
         sm_scale = D ** -0.5
     g = q.shape[1] // k.shape[1]
-    k_s, km = smooth_k(k)
+    k_s, km = smooth_k(k) if smooth else (k, torch.zeros_like(k[..., :1, :]))
     q_pad = pad_tokens(q)
     if per_block_mean:
         q_s, qm = q_block_mean(q_pad)
