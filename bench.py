@@ -193,12 +193,11 @@ def main():
     q, k, v = gen_inputs(w, seed=1234 + rank, device=dev)
     flops = attn_flops(B, Hq, N, N, D, causal)
     sm_scale = D ** -0.5
-    ds_scale = sm_scale * 1.4426950408889634
 
     def step_split(evs=None):
         if evs:
             evs[0].record()
-        z = sa.quantize_qkv(q, k, v, delta_s_scale=ds_scale)
+        z = sa.quantize_qkv(q, k, v)
         if evs:
             evs[1].record()
         o = sa.fp4_attention(z, sm_scale=sm_scale, is_causal=causal)

@@ -73,7 +73,7 @@ typedef struct {
   size_t vt_sf;     /* u8  [B,Hkv,Tk,2,512]             scales over 16 consecutive tokens          */
   size_t qm;        /* bf16 [B,Hq,Tq,D]  (per-block mean)  or [B,Hq,1,D] (whole-sequence mean)     */
   size_t km;        /* bf16 [B,Hkv,D]                                                              */
-  size_t delta_s;   /* fp32 [B,Hq,Tq or 1,Tk*128]                                                  */
+  size_t delta_s;   /* bf16 [B,Hq,Tq or 1,Tk*128]                                                  */
   size_t scratch;   /* reduction scratch of the channel-mean kernel                               */
   size_t status;    /* one int32 on the device                                                    */
   size_t workspace; /* all of the above packed (256-byte aligned parts), for sage3_attention      */
@@ -90,8 +90,7 @@ typedef struct {
   void *q_codes, *q_sf, *k_codes, *k_sf, *vt_codes, *vt_sf;
   void* qm;                  /* out: Q means (needed when per_block_mean >= 0)                       */
   void* km;                  /* out: K means (needed when smooth_k and km_in == NULL)                */
-  void* delta_s;             /* out, optional: delta_s_scale * bf16(qm . k_smoothed^T) as fp32       */
-  float delta_s_scale;
+  void* delta_s;             /* out, optional: bf16(qm . k_smoothed^T), bf16 [B,Hq,Tq or 1,Tk*128]   */
   void* scratch;             /* >= sage3_sizes.scratch bytes, 256-byte aligned                       */
   size_t scratch_bytes;
 } sage3_quant_args;
@@ -99,7 +98,7 @@ typedef struct {
 typedef struct {
   sage3_shape shape;
   const void *q_codes, *q_sf, *k_codes, *k_sf, *vt_codes, *vt_sf;   /* layouts of sage3_sizes        */
-  const float* delta_s;      /* optional; must already be multiplied by sm_scale * log2(e)          */
+  const void* delta_s;       /* optional bf16 [B,Hq,delta_s_rows,Tk*128], added to the raw scores    */
   int32_t delta_s_rows;      /* Tq, or 1 when one row serves all query blocks                        */
   void* out;                 /* bf16, strides below (elements), last dim contiguous                  */
   int64_t out_stride_b, out_stride_h, out_stride_n;

@@ -35,7 +35,7 @@ class QuantArgs(C.Structure):
                 ("km_in", C.c_void_p), ("qm_in", C.c_void_p),
                 ("q_codes", C.c_void_p), ("q_sf", C.c_void_p), ("k_codes", C.c_void_p), ("k_sf", C.c_void_p),
                 ("vt_codes", C.c_void_p), ("vt_sf", C.c_void_p),
-                ("qm", C.c_void_p), ("km", C.c_void_p), ("delta_s", C.c_void_p), ("delta_s_scale", C.c_float),
+                ("qm", C.c_void_p), ("km", C.c_void_p), ("delta_s", C.c_void_p),
                 ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t)]
 
 

@@ -84,13 +84,13 @@ class QuantizedQKV:
 
 
 def quantize_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",
-                 per_block_mean: Optional[bool] = True, smooth_k: bool = True, delta_s_scale: Optional[float] = 1.0,
+                 per_block_mean: Optional[bool] = True, smooth_k: bool = True, with_delta_s: bool = True,
                  km: Optional[torch.Tensor] = None, qm_fp32: Optional[torch.Tensor] = None) -> QuantizedQKV:
     """Smoothing + NVFP4 quantisation of Q, K, V in one fused launch.
 
     Stands in for ``preprocess_qkv`` + ``scale_and_quant_fp4`` / ``_permute`` / ``_transpose`` of
     ``sageattn4/api.py:112-229``.  ``per_block_mean``: True = per-128-token Q mean, False = whole
-    sequence Q mean, None = leave Q as is.  ``delta_s_scale=None`` skips delta_s.  ``km`` / ``qm_fp32``
+    sequence Q mean, None = leave Q as is.  ``with_delta_s=False`` skips delta_s.  ``km`` / ``qm_fp32``
     let a caller supply the means (used by the parity tests to separate rounding of the means from
     the quantiser).
     """
@@ -118,8 +118,8 @@ def quantize_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layou
     ds_rows = Tq if pbm == 1 else 1
     if pbm >= 0:
         out.qm = torch.empty((B, Hq, ds_rows, D), dtype=torch.bfloat16, device=dev)
-        if delta_s_scale is not None:
-            out.delta_s = torch.empty((B, Hq, ds_rows, Tk * 128), dtype=torch.float32, device=dev)
+        if with_delta_s:
+            out.delta_s = torch.empty((B, Hq, ds_rows, Tk * 128), dtype=torch.bfloat16, device=dev)
             out.delta_s_rows = ds_rows
     if smooth_k:
         out.km = km.contiguous() if km is not None else torch.empty((B, Hkv, D), dtype=torch.bfloat16, device=dev)
@@ -138,7 +138,6 @@ def quantize_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layou
     a.qm = out.qm.data_ptr() if out.qm is not None else None
     a.km = out.km.data_ptr() if out.km is not None else None
     a.delta_s = out.delta_s.data_ptr() if out.delta_s is not None else None
-    a.delta_s_scale = float(delta_s_scale) if delta_s_scale is not None else 1.0
     a.scratch, a.scratch_bytes = scratch.data_ptr(), scratch.numel()
     with torch.cuda.device(dev):
         _lib.check(lib.sage3_quant_qkv(C.byref(a), _stream_ptr(dev)), "sage3_quant_qkv")
@@ -148,8 +147,7 @@ def quantize_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layou
 def fp4_attention(qz: QuantizedQKV, sm_scale: Optional[float] = None, is_causal: bool = False,
                   tensor_layout: str = "HND", return_lse: bool = False, check_status: bool = False):
     """Attention on quantised operands (``blockscaled_fp4_attn``, ``sageattn4/api.py:231-243`` ->
-    ``mha_fwd``, ``blackwell/api.cpp:258``).  ``qz.delta_s`` must have been produced with
-    ``delta_s_scale = sm_scale * log2(e)``."""
+    ``mha_fwd``, ``blackwell/api.cpp:258``)."""
     lib = _lib.load()
     B, Hq, Hkv, Nq, Nk, D = qz.shape
     dev = qz.q_codes.device

@@ -13,22 +13,25 @@
 //   O /= l, bf16                                      softmax_fused.h:156-173, fwd_epilogue.cu:103-147
 // Key tiles are visited from the last to the first as the reference does (fwd_mainloop.cu:575).
 //
-// CTA = one 128-row query tile of one head.  8 warps:
-//   warps 0-3  softmax: thread r owns score row r (tensor-memory lane r) and the O row in registers
-//   warp  4    TMA producer (Q once, then a ring of K / V stages; scale factors and the delta_s
-//              row by plain bulk copies)
-//   warp  5    MMA issuer (one elected lane): tcgen05.cp of scale factors, 2x QK MMA, 2x PV MMA
-//   warps 6-7  idle (they keep the softmax warps a whole warpgroup for setmaxnreg)
-// Two CTAs are resident per SM: while one waits for its MMAs the other runs softmax.
+// One CTA per SM works on TWO adjacent 128-row query tiles of one head, which share every K / V
+// tile.  12 warps:
+//   warps 0-3   softmax warpgroup of query tile 0: thread r owns score row r (tensor-memory lane r)
+//               and the O row in registers
+//   warps 4-7   the same for query tile 1; the two warpgroups run half a period apart, so one does
+//               softmax arithmetic while the other waits for its MMAs
+//   warp  8     TMA producer (Q tiles once, then a ring of K and V stages; scale factors and the
+//               delta_s rows by plain bulk copies)
+//   warp  9     MMA issuer (one lane): tcgen05.cp of scale factors, QK and PV MMAs for both tiles
+//   warp 10     turns each delta_s row (128 bf16) into the B operand of a rank-1 bf16 MMA
+//               (ones x delta_s) that initialises the score accumulator, so the softmax warps never
+//               touch delta_s
+//   warp 11     idle (completes the warpgroup that hands its registers to the softmax warps)
 //
-// Tensor memory (256 columns per CTA): [0,128) scores S, [128,128+D) the per-tile P.V product.
-// The scale factors of the QK MMA live in the first 16 columns of the P.V region and those of the
-// PV MMA in the first 16 columns of the S region; the issue order makes that safe (QK of tile j+1
-// is issued only after the softmax warps have drained the P.V product of tile j, and PV of tile j
-// only after they have consumed S of tile j).
+// Tensor memory (512 columns): S0 [0,128) S1 [128,256) PV product [256,256+D) (shared by both
+// tiles, drained into registers right after each PV MMA) and 48 columns of scale factors.
 //
-// Every wait on an mbarrier is bounded; if one gives up the CTA records a code in *status and
-// runs to its end without further waiting, so a mistake cannot hang the GPU.
+// Every wait on an mbarrier is bounded; if one gives up the CTA records a code in *status, waits
+// (bounded) for its own copies and MMAs in flight, frees its tensor memory and returns.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -41,7 +44,7 @@ namespace {
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
 constexpr int kStages = 3;
-constexpr int kAttnThreads = 256;
+constexpr int kAttnThreads = 384;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLog2Inv2688 = -11.392317422778762f;   // log2(1 / (448 * 6))  softmax_fused.h:33
 constexpr float kLog2Inv6 = -2.584962500721156f;       // log2(1 / 6)          softmax_fused.h:34
@@ -51,41 +54,46 @@ struct Smem {
   static constexpr int kQBytes = kBlockM * D / 2;
   static constexpr int kKBytes = kBlockN * D / 2;
   static constexpr int kVBytes = D * kBlockN / 2;
-  static constexpr int kSfRow = (D / 64) * 512;         // Q / K scales per tile
-  static constexpr int kSfV = 1024;                      // V^T scales per tile
-  // offsets (all 1024-byte aligned tiles first)
-  static constexpr int q = 0;
-  static constexpr int k = q + kQBytes;
-  static constexpr int v = k + kStages * kKBytes;
-  static constexpr int p = v + kStages * kVBytes;        // P^ codes, 128 rows x 64 bytes
-  static constexpr int sfq = p + kBlockM * kBlockN / 2;
-  static constexpr int sfk = sfq + 1024;
-  static constexpr int sfv = sfk + kStages * 1024;
-  static constexpr int sfp = sfv + kStages * 1024;
-  static constexpr int ds = sfp + 1024;                  // delta_s rows, 128 fp32 per stage
-  static constexpr int bars = ds + kStages * 512;
-  static constexpr int total = bars + 256;
+  static constexpr int kPBytes = kBlockM * kBlockN / 2;
+  static constexpr int kSfRow = (D / 64) * 512;          // Q / K scales per tile
+  static constexpr int kSfV = 1024;                       // V^T scales per tile
+  static constexpr int q = 0;                             // [2]
+  static constexpr int k = q + 2 * kQBytes;               // [kStages]
+  static constexpr int v = k + kStages * kKBytes;         // [kStages]
+  static constexpr int p = v + kStages * kVBytes;         // [2]  P^ codes, 128 rows x 64 bytes
+  static constexpr int sfq = p + 2 * kPBytes;             // [2][1024]
+  static constexpr int sfk = sfq + 2 * 1024;              // [kStages][1024]
+  static constexpr int sfv = sfk + kStages * 1024;        // [kStages][1024]
+  static constexpr int sfp = sfv + kStages * 1024;        // [2][1024]
+  static constexpr int a1 = sfp + 2 * 1024;               // rank-1 A operand: column 0 = 1.0 (bf16)
+  static constexpr int b1 = a1 + 2048;                    // [kStages][2][2048] rank-1 B operands
+  static constexpr int zero = b1 + kStages * 2 * 2048;    // second K chunk of every rank-1 operand; it must lie
+                                                          // ABOVE them: the descriptor offset to it is unsigned
+  static constexpr int dsraw = zero + 2048;               // [kStages][2][256] delta_s rows as loaded
+  static constexpr int bars = dsraw + kStages * 2 * 256;
+  static constexpr int total = bars + 512;
 };
 
 struct Bars {            // byte offsets inside the barrier block
-  static constexpr int q_full = 0;
-  static constexpr int k_full = 8;                       // [kStages]
+  static constexpr int q_full = 0;                        // [2]
+  static constexpr int k_full = 16;                       // [kStages]
   static constexpr int k_empty = k_full + 8 * kStages;
   static constexpr int v_full = k_empty + 8 * kStages;
   static constexpr int v_empty = v_full + 8 * kStages;
-  static constexpr int s_full = v_empty + 8 * kStages;
-  static constexpr int p_full = s_full + 8;
-  static constexpr int o_full = p_full + 8;
-  static constexpr int o_free = o_full + 8;
-  static constexpr int drain = o_free + 8;               // MMA warp's last commit when giving up
-  static constexpr int tmem_slot = drain + 8;            // u32 written by tcgen05.alloc
+  static constexpr int ds_ready = v_empty + 8 * kStages;
+  static constexpr int s_full = ds_ready + 8 * kStages;   // [2]
+  static constexpr int p_full = s_full + 16;              // [2]
+  static constexpr int o_full = p_full + 16;              // [2]
+  static constexpr int o_free = o_full + 16;
+  static constexpr int drain = o_free + 8;                // MMA warp's last commit when giving up
+  static constexpr int tmem_slot = drain + 8;             // u32 written by tcgen05.alloc
   static constexpr int abort_flag = tmem_slot + 8;
   static constexpr int run_flag = abort_flag + 4;
 };
 
 struct KParams {
   const uint8_t *q_sf, *k_sf, *vt_sf;
-  const float* ds;
+  const __nv_bfloat16* ds;
   __nv_bfloat16* out;
   float* lse;
   int* status;
@@ -105,10 +113,37 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
   return false;
 }
 
-__device__ __forceinline__ float fmax3(float a, float b, float c) { return fmaxf(fmaxf(a, b), c); }
+// ---- packed fp32x2 arithmetic (one issue slot for two elements) and 3-input max
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(reinterpret_cast<uint64_t&>(d))
+      : "l"(reinterpret_cast<uint64_t&>(a)), "l"(reinterpret_cast<uint64_t&>(b)), "l"(reinterpret_cast<uint64_t&>(c)));
+  return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("add.rn.f32x2 %0, %1, %2;"
+      : "=l"(reinterpret_cast<uint64_t&>(d))
+      : "l"(reinterpret_cast<uint64_t&>(a)), "l"(reinterpret_cast<uint64_t&>(b)));
+  return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float max16(const uint32_t* r) {
+  const float a = fmax3(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]));
+  const float b = fmax3(__uint_as_float(r[3]), __uint_as_float(r[4]), __uint_as_float(r[5]));
+  const float c = fmax3(__uint_as_float(r[6]), __uint_as_float(r[7]), __uint_as_float(r[8]));
+  const float d = fmax3(__uint_as_float(r[9]), __uint_as_float(r[10]), __uint_as_float(r[11]));
+  const float e = fmax3(__uint_as_float(r[12]), __uint_as_float(r[13]), __uint_as_float(r[14]));
+  return fmaxf(fmax3(a, b, c), fmax3(d, e, __uint_as_float(r[15])));
+}
 
 template <int D, bool kCausal>
-__global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
+__global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                                                                    const __grid_constant__ CUtensorMap tm_k,
                                                                    const __grid_constant__ CUtensorMap tm_v,
                                                                    const KParams P) {
@@ -123,32 +158,47 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const __grid_
   volatile int* abort_s = reinterpret_cast<volatile int*>(smem + L::bars + Bars::abort_flag);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // tile coordinates: query tiles of one head are adjacent in the grid (they share K/V in L2);
-  // the longest causal tiles start first
+  // CTA -> (batch, head, pair of query tiles).  Pairs of one head are adjacent in the grid (they
+  // share K/V in L2); the longest causal pairs start first.
+  const int n_pairs = (P.Tq + 1) >> 1;
   const int bid = blockIdx.x;
-  const int qt = P.Tq - 1 - (bid % P.Tq);
-  const int bh = bid / P.Tq, b = bh / P.Hq, hq = bh % P.Hq;
+  const int pair = n_pairs - 1 - (bid % n_pairs);
+  const int bh = bid / n_pairs, b = bh / P.Hq, hq = bh % P.Hq;
   const int hkv = hq / (P.Hq / P.Hkv);
-  const int q0 = qt * kBlockM;
+  const bool has_ds = P.ds != nullptr;
 
-  int n_tiles = P.Tk;
-  if (kCausal) {
-    const int q_end = min(q0 + kBlockM, P.Nq);
-    const int lim = q_end + P.Nk - P.Nq;                   // keys [0, lim) can be visible
-    n_tiles = lim <= 0 ? 0 : min(P.Tk, (lim + kBlockN - 1) / kBlockN);
+  int n_t[2];            // key tiles each query tile visits (0: none / tile does not exist)
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int qt = 2 * pair + t;
+    int n = 0;
+    if (qt < P.Tq) {
+      n = P.Tk;
+      if (kCausal) {
+        const int q_end = min((qt + 1) * kBlockM, P.Nq);
+        const int lim = q_end + P.Nk - P.Nq;               // keys [0, lim) can be visible
+        n = lim <= 0 ? 0 : min(P.Tk, (lim + kBlockN - 1) / kBlockN);
+      }
+    }
+    n_t[t] = n;
   }
+  const int n_max = max(n_t[0], n_t[1]);
 
   if (threadIdx.x == 0) {
     mbar_init(bars + Bars::q_full, 1);
+    mbar_init(bars + Bars::q_full + 8, 1);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(bars + Bars::k_full + 8 * s, 1);
-      mbar_init(bars + Bars::k_empty + 8 * s, 4);          // one lane of each softmax warp
+      mbar_init(bars + Bars::k_empty + 8 * s, 1);          // tcgen05.commit
       mbar_init(bars + Bars::v_full + 8 * s, 1);
       mbar_init(bars + Bars::v_empty + 8 * s, 1);          // tcgen05.commit
+      mbar_init(bars + Bars::ds_ready + 8 * s, 1);
     }
-    mbar_init(bars + Bars::s_full, 1);
-    mbar_init(bars + Bars::p_full, 128);
-    mbar_init(bars + Bars::o_full, 1);
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(bars + Bars::s_full + 8 * t, 1);
+      mbar_init(bars + Bars::p_full + 8 * t, 128);
+      mbar_init(bars + Bars::o_full + 8 * t, 1);
+    }
     mbar_init(bars + Bars::o_free, 128);
     mbar_init(bars + Bars::drain, 1);
     // a failure reported by an earlier CTA (or an earlier launch that shares *status) stops new work
@@ -157,43 +207,64 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const __grid_
     *reinterpret_cast<volatile int*>(smem + L::bars + Bars::run_flag) = !bad;
     fence_mbar_init();
   }
-  if (warp == 5) {
-    tmem_alloc(bars + Bars::tmem_slot, 256);
+  // rank-1 operands: zero everything, then column 0 of A1 = 1.0
+  for (int i = threadIdx.x; i < (L::dsraw - L::a1) / 16; i += kAttnThreads)
+    reinterpret_cast<uint4*>(smem + L::a1)[i] = make_uint4(0, 0, 0, 0);
+  if (warp == 9) {
+    tmem_alloc(bars + Bars::tmem_slot, 512);
     tmem_relinquish();
   }
+  __syncthreads();
+  if (threadIdx.x < 128)
+    *reinterpret_cast<__nv_bfloat16*>(smem + L::a1 + (threadIdx.x >> 3) * 128 + (threadIdx.x & 7) * 16) =
+        __float2bfloat16(1.0f);
+  fence_proxy_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(smem + L::bars + Bars::tmem_slot);
-  const uint32_t tm_S = tmem, tm_O = tmem + 128;
-  const uint32_t tm_sfq = tm_O, tm_sfk = tm_O + 8;        // QK scales: inside the P.V region
-  const uint32_t tm_sfp = tm_S, tm_sfv = tm_S + 8;        // PV scales: inside the S region
+  const uint32_t tm_O = tmem + 256;
+  const uint32_t tm_sfq = tmem + 384, tm_sfk = tmem + 400, tm_sfp = tmem + 408, tm_sfv = tmem + 424;
 
   // read once after the barrier: every warp takes the same branch, so the register hand-over
   // below (setmaxnreg) is always executed by whole warpgroups
   const bool run = *reinterpret_cast<volatile int*>(smem + L::bars + Bars::run_flag) != 0;
-  if (n_tiles > 0 && run) {
-    if (warp == 4) {
-      // ------------------------------------------------------------------ TMA producer
+  if (n_max > 0 && run) {
+    if (warp >= 8) {
       asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-      if (lane == 0) {
+      if (warp == 8 && lane == 0) {
+        // ---------------------------------------------------------------- TMA producer
         prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
-        const int64_t qtile = ((int64_t)b * P.Hq + hq) * P.Tq + qt;
-        mbar_arrive_expect_tx(bars + Bars::q_full, L::kQBytes + L::kSfRow);
-        tma_load_2d(sbase + L::q, &tm_q, 0, (int)(qtile * kBlockM), bars + Bars::q_full);
-        bulk_load(sbase + L::sfq, P.q_sf + qtile * L::kSfRow, L::kSfRow, bars + Bars::q_full);
+        int64_t ds_row[2];
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          const int qt = 2 * pair + t;
+          ds_row[t] = ((int64_t)b * P.Hq + hq) * P.ds_rows + (P.ds_rows == 1 ? 0 : qt);
+          if (n_t[t] > 0) {
+            const int64_t qtile = ((int64_t)b * P.Hq + hq) * P.Tq + qt;
+            const uint32_t qb = bars + Bars::q_full + 8 * t;
+            mbar_arrive_expect_tx(qb, L::kQBytes + L::kSfRow);
+            tma_load_2d(sbase + L::q + t * L::kQBytes, &tm_q, 0, (int)(qtile * kBlockM), qb);
+            bulk_load(sbase + L::sfq + t * 1024, P.q_sf + qtile * L::kSfRow, L::kSfRow, qb);
+          }
+        }
         const int64_t kvhead = ((int64_t)b * P.Hkv + hkv) * P.Tk;
-        const int64_t ds_row = ((int64_t)b * P.Hq + hq) * P.ds_rows + (P.ds_rows == 1 ? 0 : qt);
         int issued = 0;
-        for (int it = 0; it < n_tiles; ++it) {
-          const int j = n_tiles - 1 - it, s = it % kStages;
+        for (int it = 0; it < n_max; ++it) {
+          const int j = n_max - 1 - it, s = it % kStages;
           const uint32_t ph = ((it / kStages) & 1) ^ 1;
           if (!wait_bar(bars + Bars::k_empty + 8 * s, ph, abort_s, P.status, 10)) break;
           const uint32_t kb = bars + Bars::k_full + 8 * s;
-          mbar_arrive_expect_tx(kb, L::kKBytes + L::kSfRow + (P.ds ? 512 : 0));
+          const int nds = has_ds ? (int)(j < n_t[0]) + (int)(j < n_t[1]) : 0;
+          mbar_arrive_expect_tx(kb, L::kKBytes + L::kSfRow + 256 * nds);
           tma_load_2d(sbase + L::k + s * L::kKBytes, &tm_k, 0, (int)((kvhead + j) * kBlockN), kb);
           bulk_load(sbase + L::sfk + s * 1024, P.k_sf + (kvhead + j) * L::kSfRow, L::kSfRow, kb);
-          if (P.ds) bulk_load(sbase + L::ds + s * 512, P.ds + (ds_row * P.Tk + j) * kBlockN, 512, kb);
+          if (has_ds) {
+#pragma unroll
+            for (int t = 0; t < 2; ++t)
+              if (j < n_t[t])
+                bulk_load(sbase + L::dsraw + (s * 2 + t) * 256, P.ds + (ds_row[t] * P.Tk + j) * kBlockN, 256, kb);
+          }
           if (!wait_bar(bars + Bars::v_empty + 8 * s, ph, abort_s, P.status, 11)) break;
           const uint32_t vb = bars + Bars::v_full + 8 * s;
           mbar_arrive_expect_tx(vb, L::kVBytes + L::kSfV);
@@ -203,56 +274,134 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const __grid_
         }
         if (*abort_s) {
           // giving up: the copies this thread started must land before the CTA may exit
-          mbar_wait(bars + Bars::q_full, 0, 1u << 20);
+          for (int t = 0; t < 2; ++t)
+            if (n_t[t] > 0) mbar_wait(bars + Bars::q_full + 8 * t, 0, 1u << 20);
           for (int it = max(0, issued - kStages); it < issued; ++it) {
             mbar_wait(bars + Bars::k_full + 8 * (it % kStages), (it / kStages) & 1, 1u << 20);
             mbar_wait(bars + Bars::v_full + 8 * (it % kStages), (it / kStages) & 1, 1u << 20);
           }
         }
-      }
-    } else if (warp == 5) {
-      // ------------------------------------------------------------------ MMA issuer
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-      if (lane == 0) {
+      } else if (warp == 10 && has_ds) {
+        // ---------------------------------------------------------------- delta_s -> rank-1 B operand
+        // B1 is a K-major [128 keys x 16] bf16 operand in 8x16-byte core matrices: key n's first
+        // element sits at (n/8)*128 + (n%8)*16; everything else stays zero.
+        for (int it = 0; it < n_max; ++it) {
+          const int j = n_max - 1 - it, s = it % kStages;
+          if (!wait_bar(bars + Bars::k_full + 8 * s, (it / kStages) & 1, abort_s, P.status, 40)) break;
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            if (j < n_t[t]) {
+              const uint2 raw = *reinterpret_cast<const uint2*>(smem + L::dsraw + (s * 2 + t) * 256 + lane * 8);
+              uint8_t* dst = smem + L::b1 + (s * 2 + t) * 2048 + (lane >> 1) * 128 + (lane & 1) * 64;   // keys 4*lane..+3
+              *reinterpret_cast<uint16_t*>(dst + 0) = (uint16_t)(raw.x & 0xFFFFu);
+              *reinterpret_cast<uint16_t*>(dst + 16) = (uint16_t)(raw.x >> 16);
+              *reinterpret_cast<uint16_t*>(dst + 32) = (uint16_t)(raw.y & 0xFFFFu);
+              *reinterpret_cast<uint16_t*>(dst + 48) = (uint16_t)(raw.y >> 16);
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bars + Bars::ds_ready + 8 * s);
+        }
+      } else if (warp == 9 && lane == 0) {
+        // ---------------------------------------------------------------- MMA issuer
         constexpr uint32_t idesc_qk = make_idesc_nvf4(kBlockM, kBlockN);
         constexpr uint32_t idesc_pv = make_idesc_nvf4(kBlockM, D);
-        bool ok = wait_bar(bars + Bars::q_full, 0, abort_s, P.status, 20);
-        for (int it = 0; ok && it < n_tiles; ++it) {
+        constexpr uint32_t idesc_r1 = make_idesc_bf16(kBlockM, kBlockN);
+        bool ok = true;
+        int pv_cnt[2] = {0, 0}, pv_total = 0;
+        bool q_ready[2] = {false, false};
+        auto active = [&](int t, int it) { return (n_max - 1 - it) < n_t[t]; };
+        // S_t = delta_s + Q_t K^T for iteration `it` (K stage must be resident)
+        auto issue_qk = [&](int t, int it, bool first_of_it) -> bool {
+          const int s = it % kStages;
+          if (!q_ready[t]) {
+            if (!wait_bar(bars + Bars::q_full + 8 * t, 0, abort_s, P.status, 20)) return false;
+            q_ready[t] = true;
+            tc_fence_after();
+#pragma unroll
+            for (int kb = 0; kb < kKB; ++kb)
+              tc_cp_sf(tm_sfq + 8 * t + 4 * kb, make_smem_desc(sbase + L::sfq + t * 1024 + kb * 512, 128, 0, 0));
+          }
+          if (first_of_it) {
+#pragma unroll
+            for (int kb = 0; kb < kKB; ++kb)
+              tc_cp_sf(tm_sfk + 4 * kb, make_smem_desc(sbase + L::sfk + s * 1024 + kb * 512, 128, 0, 0));
+          }
+          const uint32_t tm_S = tmem + 128 * t;
+          if (has_ds) {
+            const uint32_t a1 = sbase + L::a1, b1 = sbase + L::b1 + (s * 2 + t) * 2048, z = sbase + L::zero;
+            tc_mma_bf16(tm_S, make_smem_desc(a1, 128, z - a1, 0), make_smem_desc(b1, 128, z - b1, 0), idesc_r1, 0);
+          }
+#pragma unroll
+          for (int kb = 0; kb < kKB; ++kb) {
+            const uint64_t da = make_smem_desc(sbase + L::q + t * L::kQBytes + kb * 32, kSboQK, 16, kSwzQK);
+            const uint64_t db = make_smem_desc(sbase + L::k + s * L::kKBytes + kb * 32, kSboQK, 16, kSwzQK);
+            tc_mma_nvf4(tm_S, da, db, idesc_qk, tm_sfq + 8 * t + 4 * kb, tm_sfk + 4 * kb, (has_ds || kb > 0) ? 1u : 0u);
+          }
+          tc_commit(bars + Bars::s_full + 8 * t);
+          return true;
+        };
+        auto wait_k = [&](int it) -> bool {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
-          // S = Q K^T
-          if (!(ok = wait_bar(bars + Bars::k_full + 8 * s, ph, abort_s, P.status, 21))) break;
-          if (it > 0 && !(ok = wait_bar(bars + Bars::o_free, (it - 1) & 1, abort_s, P.status, 22))) break;
+          if (!wait_bar(bars + Bars::k_full + 8 * s, ph, abort_s, P.status, 21)) return false;
+          if (has_ds && !wait_bar(bars + Bars::ds_ready + 8 * s, ph, abort_s, P.status, 25)) return false;
           tc_fence_after();
+          return true;
+        };
+        // prologue: scores of the first key tile
+        ok = wait_k(0);
+        {
+          bool first = true;
+          for (int t = 0; ok && t < 2; ++t)
+            if (active(t, 0)) { ok = issue_qk(t, 0, first); first = false; }
+          if (ok) tc_commit(bars + Bars::k_empty);
+        }
+        for (int it = 0; ok && it < n_max; ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          const bool more = it + 1 < n_max;
+          bool v_ready = false, k_next_ready = false;
+          for (int t = 0; ok && t < 2; ++t) {
+            if (active(t, it)) {
+              // O_tile = P_t V
+              if (!(ok = wait_bar(bars + Bars::p_full + 8 * t, pv_cnt[t] & 1, abort_s, P.status, 23))) break;
+              if (!v_ready) {
+                if (!(ok = wait_bar(bars + Bars::v_full + 8 * s, ph, abort_s, P.status, 24))) break;
+                v_ready = true;
+                tc_fence_after();
 #pragma unroll
-          for (int kb = 0; kb < kKB; ++kb) {
-            tc_cp_sf(tm_sfq + 4 * kb, make_smem_desc(sbase + L::sfq + kb * 512, 128, 0, 0));
-            tc_cp_sf(tm_sfk + 4 * kb, make_smem_desc(sbase + L::sfk + s * 1024 + kb * 512, 128, 0, 0));
-          }
+                for (int kb = 0; kb < 2; ++kb)
+                  tc_cp_sf(tm_sfv + 4 * kb, make_smem_desc(sbase + L::sfv + s * 1024 + kb * 512, 128, 0, 0));
+              }
+              if (pv_total > 0 && !(ok = wait_bar(bars + Bars::o_free, (pv_total - 1) & 1, abort_s, P.status, 22))) break;
+              tc_fence_after();
 #pragma unroll
-          for (int kb = 0; kb < kKB; ++kb) {
-            const uint64_t da = make_smem_desc(sbase + L::q + kb * 32, kSboQK, 16, kSwzQK);
-            const uint64_t db = make_smem_desc(sbase + L::k + s * L::kKBytes + kb * 32, kSboQK, 16, kSwzQK);
-            tc_mma_nvf4(tm_S, da, db, idesc_qk, tm_sfq + 4 * kb, tm_sfk + 4 * kb, kb > 0);
-          }
-          tc_commit(bars + Bars::s_full);
-          // O_tile = P V
-          if (!(ok = wait_bar(bars + Bars::p_full, it & 1, abort_s, P.status, 23))) break;
-          if (!(ok = wait_bar(bars + Bars::v_full + 8 * s, ph, abort_s, P.status, 24))) break;
-          tc_fence_after();
+              for (int kb = 0; kb < 2; ++kb)
+                tc_cp_sf(tm_sfp + 8 * t + 4 * kb, make_smem_desc(sbase + L::sfp + t * 1024 + kb * 512, 128, 0, 0));
 #pragma unroll
-          for (int kb = 0; kb < 2; ++kb) {
-            tc_cp_sf(tm_sfp + 4 * kb, make_smem_desc(sbase + L::sfp + kb * 512, 128, 0, 0));
-            tc_cp_sf(tm_sfv + 4 * kb, make_smem_desc(sbase + L::sfv + s * 1024 + kb * 512, 128, 0, 0));
+              for (int kb = 0; kb < 2; ++kb) {
+                const uint64_t da = make_smem_desc(sbase + L::p + t * L::kPBytes + kb * 32, 512, 16, 4);
+                const uint64_t db = make_smem_desc(sbase + L::v + s * L::kVBytes + kb * 32, 512, 16, 4);
+                tc_mma_nvf4(tm_O, da, db, idesc_pv, tm_sfp + 8 * t + 4 * kb, tm_sfv + 4 * kb, kb > 0);
+              }
+              tc_commit(bars + Bars::o_full + 8 * t);
+              ++pv_cnt[t];
+              ++pv_total;
+              if (t == 1 || !active(1, it)) tc_commit(bars + Bars::v_empty + 8 * s);   // last PV of this stage
+            }
+            if (more && active(t, it + 1)) {
+              // S_t of the next key tile; S_t is free: its softmax warpgroup has signalled p_full
+              // for this iteration above (or this is the tile's first iteration)
+              if (!k_next_ready) {
+                if (!(ok = wait_k(it + 1))) break;
+              }
+              if (!(ok = issue_qk(t, it + 1, !k_next_ready))) break;
+              k_next_ready = true;
+              if (t == 1 || !active(1, it + 1)) tc_commit(bars + Bars::k_empty + 8 * ((it + 1) % kStages));
+            }
           }
-#pragma unroll
-          for (int kb = 0; kb < 2; ++kb) {
-            const uint64_t da = make_smem_desc(sbase + L::p + kb * 32, 512, 16, 4);
-            const uint64_t db = make_smem_desc(sbase + L::v + s * L::kVBytes + kb * 32, 512, 16, 4);
-            tc_mma_nvf4(tm_O, da, db, idesc_pv, tm_sfp + 4 * kb, tm_sfv + 4 * kb, kb > 0);
-          }
-          tc_commit(bars + Bars::v_empty + 8 * s);
-          tc_commit(bars + Bars::o_full);
         }
         if (!ok) {
           // giving up: let every MMA / scale copy already issued finish before tensor memory is freed
@@ -260,165 +409,149 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const __grid_
           mbar_wait(bars + Bars::drain, 0, 1u << 20);
         }
       }
-    } else if (warp < 4) {
+    } else {
       // ------------------------------------------------------------------ softmax + O accumulation
-      asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
-      const int row = threadIdx.x;                               // 0..127 = tensor-memory lane
-      const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-      const int qpos = q0 + row;
-      const int causal_lim = kCausal ? qpos + P.Nk - P.Nq : 0x7fffffff;   // last visible key
-      const int key_lim = min(P.Nk - 1, causal_lim);
-      const float c = P.scale_log2;
-      float O[D];
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+      const int t = warp >> 2;                                   // query tile of this warpgroup
+      const int row = threadIdx.x & 127;                         // tensor-memory lane
+      const int n_mine = n_t[t];
+      const int qt = 2 * pair + t;
+      const int q0 = qt * kBlockM, qpos = q0 + row;
+      if (n_mine > 0) {
+        const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t tm_S = tmem + 128 * t + lane_addr;
+        const int causal_lim = kCausal ? qpos + P.Nk - P.Nq : 0x7fffffff;   // last visible key
+        const int key_lim = min(P.Nk - 1, causal_lim);
+        const float c = P.scale_log2;
+        const float2 c2 = make_float2(c, c);
+        float2 O2[D / 2];
 #pragma unroll
-      for (int i = 0; i < D; ++i) O[i] = 0.f;
-      float m = -INFINITY, l = 0.f;
-      uint8_t* p_row = smem + L::p + row * 64;
-      const int swz = (row >> 1) & 3;
-      uint32_t* sfp_row = reinterpret_cast<uint32_t*>(smem + L::sfp + sf_atom_offset(row, 0));
-      bool ok = true;
+        for (int i = 0; i < D / 2; ++i) O2[i] = make_float2(0.f, 0.f);
+        float m = -INFINITY, l = 0.f;                            // m in raw score units
+        uint8_t* p_row = smem + L::p + t * L::kPBytes + row * 64;
+        const int swz = (row >> 1) & 3;
+        uint32_t* sfp_row = reinterpret_cast<uint32_t*>(smem + L::sfp + t * 1024 + sf_atom_offset(row, 0));
+        const uint32_t bar_s = bars + Bars::s_full + 8 * t, bar_p = bars + Bars::p_full + 8 * t;
+        const uint32_t bar_o = bars + Bars::o_full + 8 * t;
+        bool ok = true;
 
-      for (int it = 0; it < n_tiles; ++it) {
-        const int j = n_tiles - 1 - it, s = it % kStages;
-        const int n0 = j * kBlockN;
-        const bool need_mask = (n0 + kBlockN - 1 >= P.Nk) || (kCausal && n0 + kBlockN - 1 > q0 + P.Nk - P.Nq);
-        if (!(ok = wait_bar(bars + Bars::s_full, it & 1, abort_s, P.status, 30))) break;
-        tc_fence_after();
-        const float4* dsv = reinterpret_cast<const float4*>(smem + L::ds + s * 512);
-        const bool has_ds = P.ds != nullptr;
+        for (int it = 0; it < n_mine; ++it) {
+          const int j = n_mine - 1 - it;
+          const int n0 = j * kBlockN;
+          const bool need_mask = (n0 + kBlockN - 1 >= P.Nk) || (kCausal && n0 + kBlockN - 1 > q0 + P.Nk - P.Nq);
+          if (!(ok = wait_bar(bar_s, it & 1, abort_s, P.status, 30))) break;
+          tc_fence_after();
 
-        // ---- pass 1: per-16-key block maxima of t = S*c + ds
-        float bm[8];
+          // ---- pass 1: per-16-key block maxima of the raw scores
+          float bm[8];
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint32_t r[32];
-          tmem_ld32(tm_S + lane_addr + ch * 32, r);
-          tmem_wait_ld();
-          float t[32];
+          for (int ch = 0; ch < 4; ++ch) {
+            uint32_t r[32];
+            tmem_ld32(tm_S + ch * 32, r);
+            tmem_wait_ld();
+            if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            float4 d4 = has_ds ? dsv[ch * 8 + i] : make_float4(0.f, 0.f, 0.f, 0.f);
-            t[4 * i + 0] = fmaf(__uint_as_float(r[4 * i + 0]), c, d4.x);
-            t[4 * i + 1] = fmaf(__uint_as_float(r[4 * i + 1]), c, d4.y);
-            t[4 * i + 2] = fmaf(__uint_as_float(r[4 * i + 2]), c, d4.z);
-            t[4 * i + 3] = fmaf(__uint_as_float(r[4 * i + 3]), c, d4.w);
+              for (int i = 0; i < 32; ++i)
+                if (n0 + ch * 32 + i > key_lim) r[i] = 0xff800000u;
+            }
+            bm[ch * 2 + 0] = max16(r);
+            bm[ch * 2 + 1] = max16(r + 16);
           }
-          if (need_mask) {
+          const float m_new = fmaxf(fmax3(fmax3(bm[0], bm[1], bm[2]), fmax3(bm[3], bm[4], bm[5]), fmax3(bm[6], bm[7], m)), m);
+          const float m_fin = (m_new == -INFINITY) ? 0.f : m_new;
+          const float alpha = ex2_approx((m - m_fin) * c);          // 0 on the first tile
+          const float off = fmaf(m_fin, c, kLog2Inv2688);           // P = 2^(s*c - off) in (0, 2688]
+          m = m_new;
+          // per-block scale (P blockmax / 6), stored as E4M3 for the PV MMA
+          float sb[8];
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (n0 + ch * 32 + i > key_lim) t[i] = -INFINITY;
-          }
-#pragma unroll
-          for (int hb = 0; hb < 2; ++hb) {
-            float a = fmax3(t[hb * 16 + 0], t[hb * 16 + 1], t[hb * 16 + 2]);
-            float b2 = fmax3(t[hb * 16 + 3], t[hb * 16 + 4], t[hb * 16 + 5]);
-            float c2 = fmax3(t[hb * 16 + 6], t[hb * 16 + 7], t[hb * 16 + 8]);
-            float d2 = fmax3(t[hb * 16 + 9], t[hb * 16 + 10], t[hb * 16 + 11]);
-            float e2 = fmax3(t[hb * 16 + 12], t[hb * 16 + 13], t[hb * 16 + 14]);
-            bm[ch * 2 + hb] = fmaxf(fmax3(a, b2, c2), fmax3(d2, e2, t[hb * 16 + 15]));
-          }
-        }
-        const float m_new = fmaxf(fmaxf(fmax3(bm[0], bm[1], bm[2]), fmax3(bm[3], bm[4], bm[5])), fmax3(bm[6], bm[7], m));
-        const float m_fin = (m_new == -INFINITY) ? 0.f : m_new;
-        const float alpha = ex2_approx(m - m_fin);                 // 0 on the first tile
-        const float off = m_fin + kLog2Inv2688;                    // P = 2^(t - off) in (0, 2688]
-        m = m_new;
-        // per-block scale (P blockmax / 6) and the exponent offset that yields P / scale directly
-        float sb[8], boff[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          sb[i] = ex2_approx(bm[i] - off + kLog2Inv6);
-          boff[i] = (bm[i] == -INFINITY) ? 0.f : bm[i] + kLog2Inv6;
-        }
-        sfp_row[0] = f32x2_to_e4m3x2(sb[0], sb[1]) | (f32x2_to_e4m3x2(sb[2], sb[3]) << 16);
-        sfp_row[128] = f32x2_to_e4m3x2(sb[4], sb[5]) | (f32x2_to_e4m3x2(sb[6], sb[7]) << 16);
+          for (int i = 0; i < 8; ++i) sb[i] = ex2_approx(fmaf(bm[i], c, kLog2Inv6) - off);
+          sfp_row[0] = f32x2_to_e4m3x2(sb[0], sb[1]) | (f32x2_to_e4m3x2(sb[2], sb[3]) << 16);
+          sfp_row[128] = f32x2_to_e4m3x2(sb[4], sb[5]) | (f32x2_to_e4m3x2(sb[6], sb[7]) << 16);
 
-        // ---- pass 2: P / scale = 2^(t - boff) in [0, 6] -> E2M1; row sum from the unrounded values
-        float lsum = 0.f;
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint32_t r[32];
-          tmem_ld32(tm_S + lane_addr + ch * 32, r);
-          tmem_wait_ld();
+          // ---- pass 2, one 16-key block at a time: P / scale = 2^(s*c - (bm*c + log2(1/6))) in [0, 6]
+          // -> E2M1; the row sum uses the unrounded values times the unrounded block scale
+          float lsum = 0.f;
           uint32_t code[4];
 #pragma unroll
-          for (int hb = 0; hb < 2; ++hb) {
-            float pn[16];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              float4 d4 = has_ds ? dsv[ch * 8 + hb * 4 + i] : make_float4(0.f, 0.f, 0.f, 0.f);
-              pn[4 * i + 0] = fmaf(__uint_as_float(r[hb * 16 + 4 * i + 0]), c, d4.x);
-              pn[4 * i + 1] = fmaf(__uint_as_float(r[hb * 16 + 4 * i + 1]), c, d4.y);
-              pn[4 * i + 2] = fmaf(__uint_as_float(r[hb * 16 + 4 * i + 2]), c, d4.z);
-              pn[4 * i + 3] = fmaf(__uint_as_float(r[hb * 16 + 4 * i + 3]), c, d4.w);
-            }
+          for (int blk = 0; blk < 8; ++blk) {
+            uint32_t r[16];
+            tmem_ld16(tm_S + blk * 16, r);
+            tmem_wait_ld();
             if (need_mask) {
 #pragma unroll
               for (int i = 0; i < 16; ++i)
-                if (n0 + ch * 32 + hb * 16 + i > key_lim) pn[i] = -INFINITY;
+                if (n0 + blk * 16 + i > key_lim) r[i] = 0xff800000u;
             }
-            const float bo = boff[ch * 2 + hb];
-            float bs = 0.f;
+            const float nb = (bm[blk] == -INFINITY) ? 0.f : -fmaf(bm[blk], c, kLog2Inv6);
+            const float2 nb2 = make_float2(nb, nb);
+            float2 e[8];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              pn[i] = ex2_approx(pn[i] - bo);
-              bs += pn[i];
+            for (int i = 0; i < 8; ++i) {
+              e[i] = ffma2(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), c2, nb2);
+              e[i].x = ex2_approx(e[i].x);
+              e[i].y = ex2_approx(e[i].y);
             }
-            lsum = fmaf(bs, sb[ch * 2 + hb], lsum);
-            code[hb * 2 + 0] = f32x8_to_e2m1x8(pn[0], pn[1], pn[2], pn[3], pn[4], pn[5], pn[6], pn[7]);
-            code[hb * 2 + 1] = f32x8_to_e2m1x8(pn[8], pn[9], pn[10], pn[11], pn[12], pn[13], pn[14], pn[15]);
+            const float2 s4 = fadd2(fadd2(fadd2(e[0], e[1]), fadd2(e[2], e[3])), fadd2(fadd2(e[4], e[5]), fadd2(e[6], e[7])));
+            lsum = fmaf(s4.x + s4.y, sb[blk], lsum);
+            code[(blk & 1) * 2 + 0] = f32x8_to_e2m1x8(e[0].x, e[0].y, e[1].x, e[1].y, e[2].x, e[2].y, e[3].x, e[3].y);
+            code[(blk & 1) * 2 + 1] = f32x8_to_e2m1x8(e[4].x, e[4].y, e[5].x, e[5].y, e[6].x, e[6].y, e[7].x, e[7].y);
+            if (blk & 1)
+              *reinterpret_cast<uint4*>(p_row + (((blk >> 1) ^ swz) << 4)) = make_uint4(code[0], code[1], code[2], code[3]);
           }
-          *reinterpret_cast<uint4*>(p_row + ((ch ^ swz) << 4)) = make_uint4(code[0], code[1], code[2], code[3]);
-        }
-        l = fmaf(l, alpha, lsum);
-        // S consumed and P^ written: hand both to the MMA warp, release the K stage (delta_s row)
-        tc_fence_before();
-        fence_proxy_async_smem();
-        mbar_arrive(bars + Bars::p_full);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bars + Bars::k_empty + 8 * s);
+          l = fmaf(l, alpha, lsum);
+          // S consumed and P^ written: hand both to the MMA warp
+          tc_fence_before();
+          fence_proxy_async_smem();
+          mbar_arrive(bar_p);
 
-        // ---- O = O * alpha + P^ V^
-        if (!(ok = wait_bar(bars + Bars::o_full, it & 1, abort_s, P.status, 31))) break;
-        tc_fence_after();
+          // ---- O = O * alpha + P^ V^
+          if (!(ok = wait_bar(bar_o, it & 1, abort_s, P.status, 31))) break;
+          tc_fence_after();
+          const float2 al2 = make_float2(alpha, alpha);
 #pragma unroll
-        for (int ch = 0; ch < D / 32; ++ch) {
-          uint32_t r[32];
-          tmem_ld32(tm_O + lane_addr + ch * 32, r);
-          tmem_wait_ld();
+          for (int ch = 0; ch < D / 32; ++ch) {
+            uint32_t r[32];
+            tmem_ld32(tm_O + lane_addr + ch * 32, r);
+            tmem_wait_ld();
+            if (ch == D / 32 - 1) {          // product is in registers: the other tile's PV may overwrite it
+              tc_fence_before();
+              mbar_arrive(bars + Bars::o_free);
+            }
 #pragma unroll
-          for (int i = 0; i < 32; ++i) O[ch * 32 + i] = fmaf(O[ch * 32 + i], alpha, __uint_as_float(r[i]));
+            for (int i = 0; i < 16; ++i)
+              O2[ch * 16 + i] = ffma2(O2[ch * 16 + i], al2, make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])));
+          }
         }
-        tc_fence_before();
-        mbar_arrive(bars + Bars::o_free);
-      }
 
-      // ---- epilogue: O / l -> bf16 -> global (row-contiguous 16-byte stores)
-      if (ok && qpos < P.Nq) {
-        const float inv = (l == 0.f || l != l) ? 0.f : 1.0f / l;
-        __nv_bfloat16* orow = P.out + b * P.o_sb + hq * P.o_sh + (int64_t)qpos * P.o_sn;
+        // ---- epilogue: O / l -> bf16 -> global (row-contiguous 16-byte stores)
+        if (ok && qpos < P.Nq) {
+          const float inv = (l == 0.f || l != l) ? 0.f : 1.0f / l;
+          __nv_bfloat16* orow = P.out + b * P.o_sb + hq * P.o_sh + (int64_t)qpos * P.o_sn;
 #pragma unroll
-        for (int i = 0; i < D / 8; ++i) {
-          uint4 o;
-          o.x = pack_bf16(O[8 * i + 0] * inv, O[8 * i + 1] * inv);
-          o.y = pack_bf16(O[8 * i + 2] * inv, O[8 * i + 3] * inv);
-          o.z = pack_bf16(O[8 * i + 4] * inv, O[8 * i + 5] * inv);
-          o.w = pack_bf16(O[8 * i + 6] * inv, O[8 * i + 7] * inv);
-          reinterpret_cast<uint4*>(orow)[i] = o;
-        }
-        if (P.lse) {
-          // natural-log sum of exp(sm_scale * s) over the row (l carries the factor 2688)
-          P.lse[((int64_t)b * P.Hq + hq) * P.Nq + qpos] =
-              (l == 0.f) ? -INFINITY : (m + log2f(l) + kLog2Inv2688) * (1.0f / kLog2e);
+          for (int i = 0; i < D / 8; ++i) {
+            uint4 o;
+            o.x = pack_bf16(O2[4 * i + 0].x * inv, O2[4 * i + 0].y * inv);
+            o.y = pack_bf16(O2[4 * i + 1].x * inv, O2[4 * i + 1].y * inv);
+            o.z = pack_bf16(O2[4 * i + 2].x * inv, O2[4 * i + 2].y * inv);
+            o.w = pack_bf16(O2[4 * i + 3].x * inv, O2[4 * i + 3].y * inv);
+            reinterpret_cast<uint4*>(orow)[i] = o;
+          }
+          if (P.lse) {
+            // natural-log sum of exp(sm_scale * s) over the row (l carries the factor 2688)
+            P.lse[((int64_t)b * P.Hq + hq) * P.Nq + qpos] =
+                (l == 0.f) ? -INFINITY : (m * c + log2f(l) + kLog2Inv2688) * (1.0f / kLog2e);
+          }
         }
       }
-    } else {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     }
-  } else if (n_tiles == 0 && warp < 4) {
-    // causal tile that sees no key at all: zeros, like the reference's store_zero (fwd_epilogue.cu:150-183)
-    const int qpos = q0 + (int)threadIdx.x;
-    if (qpos < P.Nq) {
+  }
+  // query tiles that see no key at all (causal, more queries than keys): zeros, like the
+  // reference's store_zero (fwd_epilogue.cu:150-183)
+  if (run && warp < 8) {
+    const int t = warp >> 2, qt = 2 * pair + t;
+    const int qpos = qt * kBlockM + (threadIdx.x & 127);
+    if (qt < P.Tq && n_t[t] == 0 && qpos < P.Nq) {
       __nv_bfloat16* orow = P.out + b * P.o_sb + hq * P.o_sh + (int64_t)qpos * P.o_sn;
       for (int i = 0; i < D / 8; ++i) reinterpret_cast<uint4*>(orow)[i] = make_uint4(0, 0, 0, 0);
       if (P.lse) P.lse[((int64_t)b * P.Hq + hq) * P.Nq + qpos] = INFINITY;
@@ -427,7 +560,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_fwd_kernel(const __grid_
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem, 256);
+  if (warp == 9) tmem_dealloc(tmem, 512);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -475,14 +608,14 @@ cudaError_t launch(const AttnArgs& a, cudaStream_t stream) {
     return cudaErrorInvalidValue;
   KParams P;
   P.q_sf = (const uint8_t*)a.q_sf; P.k_sf = (const uint8_t*)a.k_sf; P.vt_sf = (const uint8_t*)a.vt_sf;
-  P.ds = (const float*)a.ds; P.out = (__nv_bfloat16*)a.out; P.lse = a.lse; P.status = a.status;
+  P.ds = (const __nv_bfloat16*)a.ds; P.out = (__nv_bfloat16*)a.out; P.lse = a.lse; P.status = a.status;
   P.o_sb = a.o_sb; P.o_sh = a.o_sh; P.o_sn = a.o_sn;
   P.B = a.B; P.Hq = a.Hq; P.Hkv = a.Hkv; P.Nq = a.Nq; P.Nk = a.Nk; P.Tq = Tq; P.Tk = Tk; P.ds_rows = a.ds_rows;
   P.scale_log2 = a.sm_scale * kLog2e;
   auto kern = attn_fwd_kernel<D, kCausal>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total + 1024);
   if (e != cudaSuccess) return e;
-  const int64_t grid = (int64_t)a.B * a.Hq * Tq;
+  const int64_t grid = (int64_t)a.B * a.Hq * ((Tq + 1) / 2);
   kern<<<(unsigned)grid, kAttnThreads, L::total + 1024, stream>>>(tq, tk, tv, P);
   return cudaGetLastError();
 }

@@ -72,7 +72,7 @@ int sage3_buffer_sizes(const sage3_shape* shape, int per_block_mean, sage3_sizes
   out->vt_sf = bhk * Tk * 1024;
   out->qm = bhq * ds_rows * s.D * 2;
   out->km = bhk * s.D * 2;
-  out->delta_s = per_block_mean < 0 ? 0 : bhq * ds_rows * Tk * 128 * 4;
+  out->delta_s = per_block_mean < 0 ? 0 : bhq * ds_rows * Tk * 128 * 2;
   size_t sk = sage3::quant_scratch_bytes(s.B, s.Hkv, s.Nk, s.D);
   size_t sq = sage3::quant_scratch_bytes(s.B, s.Hq, s.Nq, s.D);
   out->scratch = sk > sq ? sk : sq;
@@ -140,7 +140,6 @@ int sage3_quant_qkv(const sage3_quant_args* a, void* stream_) {
     d.qm = a->qm; d.k = a->k.ptr; d.k_sb = a->k.stride_b; d.k_sh = a->k.stride_h; d.k_sn = a->k.stride_n;
     d.km = km; d.ds = a->delta_s;
     d.B = s.B; d.Hq = s.Hq; d.Hkv = s.Hkv; d.Tq = a->per_block_mean == 1 ? Tq : 1; d.Nk = s.Nk; d.D = s.D;
-    d.out_scale = a->delta_s_scale;
     e = sage3::launch_delta_s(d, stream);
     if (e != cudaSuccess) return cuda_fail(e);
   }
@@ -196,12 +195,11 @@ int sage3_attention(const sage3_fwd_args* a, void* stream) {
   if (a->device_status) status = a->device_status;
   const float sm_scale = a->sm_scale > 0.f ? a->sm_scale : 1.0f / sqrtf((float)a->shape.D);
   q.delta_s = a->per_block_mean >= 0 ? ds : nullptr;
-  q.delta_s_scale = sm_scale * 1.4426950408889634f;
   if (int st = sage3_quant_qkv(&q, stream)) return st;
   sage3_attn_args t{};
   t.shape = a->shape;
   t.q_codes = q.q_codes; t.q_sf = q.q_sf; t.k_codes = q.k_codes; t.k_sf = q.k_sf; t.vt_codes = q.vt_codes; t.vt_sf = q.vt_sf;
-  t.delta_s = reinterpret_cast<const float*>(q.delta_s);
+  t.delta_s = q.delta_s;
   t.delta_s_rows = a->per_block_mean == 1 ? (a->shape.Nq + 127) / 128 : 1;
   t.out = a->out; t.out_stride_b = a->out_stride_b; t.out_stride_h = a->out_stride_h; t.out_stride_n = a->out_stride_n;
   t.lse = a->lse; t.sm_scale = sm_scale; t.is_causal = a->is_causal; t.device_status = status;

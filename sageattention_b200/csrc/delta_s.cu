@@ -1,16 +1,16 @@
-// delta_s[b, hq, qb, n] = out_scale * bf16( sum_d qm[b, hq, qb, d] * ks[b, hkv, n, d] ),  ks = bf16(k - km)
+// delta_s[b, hq, qb, n] = bf16( sum_d qm[b, hq, qb, d] * ks[b, hkv, n, d] ),  ks = bf16(k - km)
 //
 // Replaces `delta_s = torch.matmul(qm, k.transpose(-2, -1)).to(torch.float32)` of
-// sageattn4/api.py:201: a bf16 GEMM (fp32 accumulation, bf16 result) widened to fp32.  The
-// attention kernel adds row qb of delta_s to every score of query block qb, which restores the Q
-// block mean that was removed before quantisation; out_scale lets the caller fold the softmax
-// scale (sm_scale * log2 e) in so that the kernel needs one fused multiply-add per score.
+// sageattn4/api.py:201: a bf16 GEMM (fp32 accumulation, bf16 result) that the reference then
+// widens to fp32.  It stays bf16 here - the same values in half the bytes - because the
+// attention kernel feeds each row to the tensor core as a bf16 operand (rank-1 update of the
+// score accumulator), which restores the Q block mean that was removed before quantisation.
 //
 // One CTA per (128-key tile, kv head): the smoothed K tile is rebuilt in shared memory once and
-// multiplied against the block means of every query head of the GQA group.  The fp32 output
-// ([Tq x 128] per CTA and head) dominates the traffic, so the small contraction runs on
-// mma.sync m16n8k16 with fragments read straight from shared memory, and every quad of lanes
-// stores one full 32-byte sector.
+// multiplied against the block means of every query head of the GQA group.  The output
+// ([Tq x 128] bf16 per CTA and head) dominates the traffic, so the small contraction runs on
+// mma.sync m16n8k16 with fragments read straight from shared memory, and results are staged per
+// warp so that they leave as whole 256-byte rows.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -19,11 +19,12 @@ namespace sage3 {
 template <int D>
 __global__ void __launch_bounds__(256) delta_s_kernel(
     const __nv_bfloat16* __restrict__ qm, const __nv_bfloat16* __restrict__ k, int64_t k_sb, int64_t k_sh,
-    int64_t k_sn, const __nv_bfloat16* __restrict__ km, float* __restrict__ ds, int Hq, int Hkv, int Tq,
-    int Nk, int Nk_pad, float out_scale) {
+    int64_t k_sn, const __nv_bfloat16* __restrict__ km, __nv_bfloat16* __restrict__ ds, int Hq, int Hkv, int Tq,
+    int Nk, int Nk_pad) {
   constexpr int PITCH = D + 8;                         // bf16 elements; 4-bank skew per row
   extern __shared__ __align__(16) unsigned char dyn_smem[];
   __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(dyn_smem);              // [128][PITCH]
+  __nv_bfloat16* cs = ks + 128 * PITCH;                                        // [8 warps][16][136]
   const int tile = blockIdx.x, bh = blockIdx.y, b = bh / Hkv, hkv = bh % Hkv, G = Hq / Hkv;
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31, g = lane >> 2, tg = lane & 3;
 
@@ -69,8 +70,7 @@ __global__ void __launch_bounds__(256) delta_s_kernel(
       a[s][2] = p0 ? p0[s * 8 + 4 + tg] : 0u;
       a[s][3] = p1 ? p1[s * 8 + 4 + tg] : 0u;
     }
-    float* d0 = r0 < M ? ds + ((((int64_t)b * Hq + hkv * G + r0 / Tq) * Tq + r0 % Tq) * Nk_pad + tile * 128) : nullptr;
-    float* d1 = r1 < M ? ds + ((((int64_t)b * Hq + hkv * G + r1 / Tq) * Tq + r1 % Tq) * Nk_pad + tile * 128) : nullptr;
+    __nv_bfloat16* cw = cs + warp * (16 * 136);
 #pragma unroll 4
     for (int nt = 0; nt < 16; ++nt) {
       float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
@@ -83,30 +83,39 @@ __global__ void __launch_bounds__(256) delta_s_kernel(
             : "+f"(c0), "+f"(c1), "+f"(c2), "+f"(c3)
             : "r"(a[s][0]), "r"(a[s][1]), "r"(a[s][2]), "r"(a[s][3]), "r"(b0), "r"(b1));
       }
-      // round to bf16 (the reference GEMM's output type), then widen and pre-scale.
-      // Four lanes of a quad write one full 32-byte sector per row.
-      uint32_t p01 = pack_bf16(c0, c1), p23 = pack_bf16(c2, c3);
-      if (d0) *reinterpret_cast<float2*>(d0 + nt * 8 + tg * 2) = make_float2(bf16_lo(p01) * out_scale, bf16_hi(p01) * out_scale);
-      if (d1) *reinterpret_cast<float2*>(d1 + nt * 8 + tg * 2) = make_float2(bf16_lo(p23) * out_scale, bf16_hi(p23) * out_scale);
+      *reinterpret_cast<uint32_t*>(&cw[g * 136 + nt * 8 + tg * 2]) = pack_bf16(c0, c1);
+      *reinterpret_cast<uint32_t*>(&cw[(g + 8) * 136 + nt * 8 + tg * 2]) = pack_bf16(c2, c3);
     }
+    __syncwarp();
+    // 16 rows x 256 bytes leave as whole rows: two rows per warp store instruction
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = i * 2 + (lane >> 4), m = m0 + r;
+      if (m < M) {
+        uint4 v = *reinterpret_cast<const uint4*>(&cw[r * 136 + (lane & 15) * 8]);
+        __nv_bfloat16* dst = ds + ((((int64_t)b * Hq + hkv * G + m / Tq) * Tq + m % Tq) * Nk_pad + tile * 128);
+        reinterpret_cast<uint4*>(dst)[lane & 15] = v;
+      }
+    }
+    __syncwarp();
   }
 }
 
 cudaError_t launch_delta_s(const DeltaSArgs& a, cudaStream_t stream) {
   const int Tk = (a.Nk + 127) / 128;
   dim3 grid(Tk, a.B * a.Hkv);
-  const int smem = 128 * (a.D + 8) * 2;
+  const int smem = (128 * (a.D + 8) + 8 * 16 * 136) * 2;
   // per device and cheap, so set on every call rather than cached per process
-  cudaFuncSetAttribute(delta_s_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 136 * 2);
-  cudaFuncSetAttribute(delta_s_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 72 * 2);
+  cudaFuncSetAttribute(delta_s_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (128 * 136 + 8 * 16 * 136) * 2);
+  cudaFuncSetAttribute(delta_s_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (128 * 72 + 8 * 16 * 136) * 2);
   if (a.D == 128)
     delta_s_kernel<128><<<grid, 256, smem, stream>>>((const __nv_bfloat16*)a.qm, (const __nv_bfloat16*)a.k, a.k_sb, a.k_sh,
-                                                  a.k_sn, (const __nv_bfloat16*)a.km, (float*)a.ds, a.Hq, a.Hkv,
-                                                  a.Tq, a.Nk, Tk * 128, a.out_scale);
+                                                  a.k_sn, (const __nv_bfloat16*)a.km, (__nv_bfloat16*)a.ds, a.Hq, a.Hkv,
+                                                  a.Tq, a.Nk, Tk * 128);
   else
     delta_s_kernel<64><<<grid, 256, smem, stream>>>((const __nv_bfloat16*)a.qm, (const __nv_bfloat16*)a.k, a.k_sb, a.k_sh,
-                                                 a.k_sn, (const __nv_bfloat16*)a.km, (float*)a.ds, a.Hq, a.Hkv,
-                                                 a.Tq, a.Nk, Tk * 128, a.out_scale);
+                                                 a.k_sn, (const __nv_bfloat16*)a.km, (__nv_bfloat16*)a.ds, a.Hq, a.Hkv,
+                                                 a.Tq, a.Nk, Tk * 128);
   return cudaGetLastError();
 }
 

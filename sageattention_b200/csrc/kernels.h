@@ -27,15 +27,14 @@ struct DeltaSArgs {
   const void* k;                          // bf16 raw K, strides below
   int64_t k_sb, k_sh, k_sn;
   const void* km;                         // bf16 [B,Hkv,D] or null
-  void* ds;                               // fp32 [B,Hq,Tq,Nk_pad]
+  void* ds;                               // bf16 [B,Hq,Tq,Nk_pad]
   int B, Hq, Hkv, Tq, Nk, D;
-  float out_scale;                        // multiplies the bf16-rounded dot products
 };
 cudaError_t launch_delta_s(const DeltaSArgs& a, cudaStream_t stream);
 
 struct AttnArgs {
   const void *q_codes, *q_sf, *k_codes, *k_sf, *vt_codes, *vt_sf;
-  const void* ds;                         // fp32 [B,Hq,ds_rows,Nk_pad], already times sm_scale*log2(e); or null
+  const void* ds;                         // bf16 [B,Hq,ds_rows,Nk_pad] (raw score units) or null
   int ds_rows;                            // Tq, or 1 when one row serves every query block
   void* out;                              // bf16, strides below
   int64_t o_sb, o_sh, o_sn;

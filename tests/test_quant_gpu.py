@@ -56,7 +56,7 @@ def ref_quant_trans(ref, v):
 @pytest.mark.parametrize("N", [128, 1024, 1000, 1])
 def test_plain_quant_matches_reference_kernels(ref, D, N):
     q, k, v = U.make_qkv(2, 3, 3, N, N, D, seed=N + D, device=DEV)
-    z = sa.quantize_qkv(q, k, v, per_block_mean=None, smooth_k=False, delta_s_scale=None)
+    z = sa.quantize_qkv(q, k, v, per_block_mean=None, smooth_k=False, with_delta_s=False)
     qp, kp, vp = (sage3.pad_tokens(t) for t in (q, k, v))
     for mine, theirs in [(U.unpack_rows(z.q_codes, z.q_sf), ref_quant_rows(ref, qp)),
                          (U.unpack_rows(z.k_codes, z.k_sf), ref_quant_rows(ref, kp, permute=True)),
@@ -69,7 +69,7 @@ def test_quant_matches_cpu_oracle_device_mode():
     if nvfp4.device_tables() is None:
         pytest.skip("tests/golden/device_tables.npz not generated yet")
     q, k, v = U.make_qkv(1, 2, 2, 384, 384, 128, seed=5, device=DEV)
-    z = sa.quantize_qkv(q, k, v, per_block_mean=None, smooth_k=False, delta_s_scale=None)
+    z = sa.quantize_qkv(q, k, v, per_block_mean=None, smooth_k=False, with_delta_s=False)
     c, s = U.unpack_rows(z.q_codes, z.q_sf)
     oc, os_ = nvfp4.quantize_nvfp4(U.bf16_np(q), "device")
     assert np.array_equal(s, os_) and np.array_equal(c, oc)
@@ -82,7 +82,7 @@ def test_quant_vs_cpu_oracle_exact_mode_differs_only_rarely():
     # IEEE division (the reference's Python emulation) vs the GPU's approximate division: a code may
     # differ only where x/scale falls within an ulp of a rounding boundary.  Budget: 0.5 % of codes.
     q, k, v = U.make_qkv(1, 2, 2, 512, 512, 128, seed=6, device=DEV)
-    z = sa.quantize_qkv(q, k, v, per_block_mean=None, smooth_k=False, delta_s_scale=None)
+    z = sa.quantize_qkv(q, k, v, per_block_mean=None, smooth_k=False, with_delta_s=False)
     c, s = U.unpack_rows(z.q_codes, z.q_sf)
     oc, os_ = nvfp4.quantize_nvfp4(U.bf16_np(q), "exact")
     assert (s != os_).mean() < 5e-3
@@ -115,7 +115,7 @@ def test_smoothed_quant_with_given_means_matches_reference(ref, layout, N):
     # cuBLAS, so allow one bf16 ulp on a few entries
     ks_rep = ks.repeat_interleave(Hq // Hkv, dim=1)
     want = torch.matmul(qm32.to(torch.bfloat16), ks_rep.transpose(-2, -1)).float()
-    got = z.delta_s
+    got = z.delta_s.float()
     close = (got - want).abs() <= want.abs() * 2.0 ** -7 + 1e-6
     assert close.all() and (got != want).float().mean() < 0.02
 
