@@ -16,7 +16,9 @@
 // One CTA per SM works on TWO adjacent 128-row query tiles of one head, which share every K / V
 // tile.  12 warps:
 //   warps 0-3   softmax warpgroup of query tile 0: thread r owns score row r (tensor-memory lane r)
-//               and the O row in registers
+//               and the O row in registers.  Per key tile: pass 1 scans S for the 16-key block
+//               maxima, pass 2 turns S into P^; every tensor-memory load is issued one block ahead
+//               of its use; then the P.V product is folded into O.
 //   warps 4-7   the same for query tile 1; the two warpgroups run half a period apart, so one does
 //               softmax arithmetic while the other waits for its MMAs
 //   warp  8     TMA producer (Q tiles once, then a ring of K and V stages; scale factors and the
@@ -70,7 +72,8 @@ struct Smem {
   static constexpr int zero = b1 + kStages * 2 * 2048;    // second K chunk of every rank-1 operand; it must lie
                                                           // ABOVE them: the descriptor offset to it is unsigned
   static constexpr int dsraw = zero + 2048;               // [kStages][2][256] delta_s rows as loaded
-  static constexpr int bars = dsraw + kStages * 2 * 256;
+  static constexpr int stats = dsraw + kStages * 2 * 256; // [2][8 blocks][128 rows] float2 (exponent offset, scale)
+  static constexpr int bars = stats + 2 * 8 * 128 * 8;
   static constexpr int total = bars + 512;
 };
 
@@ -140,6 +143,103 @@ __device__ __forceinline__ float max16(const uint32_t* r) {
   const float d = fmax3(__uint_as_float(r[9]), __uint_as_float(r[10]), __uint_as_float(r[11]));
   const float e = fmax3(__uint_as_float(r[12]), __uint_as_float(r[13]), __uint_as_float(r[14]));
   return fmaxf(fmax3(a, b, c), fmax3(d, e, __uint_as_float(r[15])));
+}
+
+// One key tile for one score row (one thread): pass 1 finds the 16-key block maxima, pass 2 turns the
+// scores into E2M1 codes of P / blockscale and the row sum.  Straight-line code (no branch when kMask
+// is false) so that the scheduler can overlap the exp2 stream of one block with the adds and
+// conversions of its neighbour; every tensor-memory load is issued one block before its use.
+//   m, l      running row maximum (raw score units) and row sum (of P = 2^(s*c - m*c) * 2688)
+//   st        this thread's column of the shared scratch: per block (exponent offset, scale)
+//   returns   alpha = 2^((m_old - m_new) * c), the factor the O row must be rescaled by
+template <bool kMask>
+__device__ __forceinline__ float softmax_tile_impl(const uint32_t tm_S, const float c, float& m, float& l, float2* st,
+                                              uint32_t* sfp_row, uint8_t* p_row, const int swz, const int n0,
+                                              const int key_lim) {
+  uint32_t ra[16], rb[16];
+  float bm[8];
+  tmem_ld16(tm_S, ra);
+#pragma unroll
+  for (int blk = 0; blk < 8; blk += 2) {
+    tmem_wait_ld();
+    tmem_ld16(tm_S + (blk + 1) * 16, rb);
+    if (kMask) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) ra[i] = (n0 + blk * 16 + i > key_lim) ? 0xff800000u : ra[i];
+    }
+    bm[blk] = max16(ra);
+    tmem_wait_ld();
+    tmem_ld16(tm_S + ((blk + 2) & 7) * 16, ra);          // the last one already fetches block 0 for pass 2
+    if (kMask) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) rb[i] = (n0 + (blk + 1) * 16 + i > key_lim) ? 0xff800000u : rb[i];
+    }
+    bm[blk + 1] = max16(rb);
+  }
+  const float m_new = fmax3(fmax3(bm[0], bm[1], bm[2]), fmax3(bm[3], bm[4], bm[5]), fmax3(bm[6], bm[7], m));
+  const float m_fin = (m_new == -INFINITY) ? 0.f : m_new;
+  const float alpha = ex2_approx((m - m_fin) * c);          // 0 on the first tile
+  const float off = fmaf(m_fin, c, kLog2Inv2688);           // P = 2^(s*c - off) in (0, 2688]
+  m = m_new;
+  // per block: exponent offset that yields P / scale directly, and the scale (P blockmax / 6); parked
+  // in this thread's own shared-memory column to keep registers for the O row
+  {
+    float sb[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float e = fmaf(bm[i], c, kLog2Inv6);
+      sb[i] = ex2_approx(e - off);
+      st[i * 128] = make_float2((bm[i] == -INFINITY) ? 0.f : -e, sb[i]);
+    }
+    sfp_row[0] = f32x2_to_e4m3x2(sb[0], sb[1]) | (f32x2_to_e4m3x2(sb[2], sb[3]) << 16);
+    sfp_row[128] = f32x2_to_e4m3x2(sb[4], sb[5]) | (f32x2_to_e4m3x2(sb[6], sb[7]) << 16);
+  }
+  // ---- pass 2
+  const float2 c2 = make_float2(c, c);
+  float lsum = 0.f;
+  uint32_t code[4];
+  float2 ns = st[0];
+#pragma unroll
+  for (int blk = 0; blk < 8; ++blk) {
+    uint32_t (&r)[16] = (blk & 1) ? rb : ra;
+    uint32_t (&rn)[16] = (blk & 1) ? ra : rb;
+    tmem_wait_ld();
+    if (blk < 7) tmem_ld16(tm_S + (blk + 1) * 16, rn);
+    const float2 ns_next = st[((blk + 1) & 7) * 128];
+    if (kMask) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) r[i] = (n0 + blk * 16 + i > key_lim) ? 0xff800000u : r[i];
+    }
+    const float2 nb2 = make_float2(ns.x, ns.x);
+    float2 e[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      e[i] = ffma2(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), c2, nb2);
+      e[i].x = ex2_approx(e[i].x);
+      e[i].y = ex2_approx(e[i].y);
+    }
+    const float2 s4 = fadd2(fadd2(fadd2(e[0], e[1]), fadd2(e[2], e[3])), fadd2(fadd2(e[4], e[5]), fadd2(e[6], e[7])));
+    lsum = fmaf(s4.x + s4.y, ns.y, lsum);
+    code[(blk & 1) * 2 + 0] = f32x8_to_e2m1x8(e[0].x, e[0].y, e[1].x, e[1].y, e[2].x, e[2].y, e[3].x, e[3].y);
+    code[(blk & 1) * 2 + 1] = f32x8_to_e2m1x8(e[4].x, e[4].y, e[5].x, e[5].y, e[6].x, e[6].y, e[7].x, e[7].y);
+    if (blk & 1) *reinterpret_cast<uint4*>(p_row + (((blk >> 1) ^ swz) << 4)) = make_uint4(code[0], code[1], code[2], code[3]);
+    ns = ns_next;
+  }
+  l = fmaf(l, alpha, lsum);
+  return alpha;
+}
+
+// The unmasked tile is the hot path and is inlined; tiles that need the key-padding / causal mask are
+// rare (the last key tile, the diagonal) and go through a real call so that their extra selects do not
+// cost the hot path registers.
+__device__ __forceinline__ float softmax_tile_plain(const uint32_t tm_S, const float c, float& m, float& l, float2* st,
+                                                    uint32_t* sfp_row, uint8_t* p_row, const int swz) {
+  return softmax_tile_impl<false>(tm_S, c, m, l, st, sfp_row, p_row, swz, 0, 0);
+}
+__device__ __noinline__ float softmax_tile_masked(const uint32_t tm_S, const float c, float& m, float& l, float2* st,
+                                                  uint32_t* sfp_row, uint8_t* p_row, const int swz, const int n0,
+                                                  const int key_lim) {
+  return softmax_tile_impl<true>(tm_S, c, m, l, st, sfp_row, p_row, swz, n0, key_lim);
 }
 
 template <int D, bool kCausal>
@@ -231,7 +331,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
   const bool run = *reinterpret_cast<volatile int*>(smem + L::bars + Bars::run_flag) != 0;
   if (n_max > 0 && run) {
     if (warp >= 8) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
       if (warp == 8 && lane == 0) {
         // ---------------------------------------------------------------- TMA producer
         prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
@@ -291,12 +391,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
             if (j < n_t[t]) {
-              const uint2 raw = *reinterpret_cast<const uint2*>(smem + L::dsraw + (s * 2 + t) * 256 + lane * 8);
-              uint8_t* dst = smem + L::b1 + (s * 2 + t) * 2048 + (lane >> 1) * 128 + (lane & 1) * 64;   // keys 4*lane..+3
-              *reinterpret_cast<uint16_t*>(dst + 0) = (uint16_t)(raw.x & 0xFFFFu);
-              *reinterpret_cast<uint16_t*>(dst + 16) = (uint16_t)(raw.x >> 16);
-              *reinterpret_cast<uint16_t*>(dst + 32) = (uint16_t)(raw.y & 0xFFFFu);
-              *reinterpret_cast<uint16_t*>(dst + 48) = (uint16_t)(raw.y >> 16);
+              const uint16_t* raw = reinterpret_cast<const uint16_t*>(smem + L::dsraw + (s * 2 + t) * 256);
+              uint8_t* dst = smem + L::b1 + (s * 2 + t) * 2048 + (lane >> 3) * 128 + (lane & 7) * 16;   // keys lane + 32 i
+#pragma unroll
+              for (int i = 0; i < 4; ++i) *reinterpret_cast<uint16_t*>(dst + i * 512) = raw[lane + 32 * i];
             }
           }
           fence_proxy_async_smem();
@@ -305,44 +403,53 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         }
       } else if (warp == 9 && lane == 0) {
         // ---------------------------------------------------------------- MMA issuer
+        // This one thread paces the whole CTA, so its instruction stream is kept minimal: every
+        // shared-memory descriptor is a constant high word (stride / swizzle / version bits) plus a
+        // low word (address >> 4, leading-offset field) that only needs an integer add per use.
         constexpr uint32_t idesc_qk = make_idesc_nvf4(kBlockM, kBlockN);
         constexpr uint32_t idesc_pv = make_idesc_nvf4(kBlockM, D);
         constexpr uint32_t idesc_r1 = make_idesc_bf16(kBlockM, kBlockN);
+        constexpr uint32_t HI_QK = (kSboQK >> 4) | (1u << 14) | (kSwzQK << 29);
+        constexpr uint32_t HI_PV = (512u >> 4) | (1u << 14) | (4u << 29);
+        constexpr uint32_t HI_SF = (128u >> 4) | (1u << 14);          // 8x16-byte core matrices, no swizzle
+        constexpr uint32_t LBO1 = 1u << 16;                            // leading offset field of swizzled operands
+        const uint32_t q_lo = ((sbase + L::q) >> 4) | LBO1, k_lo = ((sbase + L::k) >> 4) | LBO1;
+        const uint32_t p_lo = ((sbase + L::p) >> 4) | LBO1, v_lo = ((sbase + L::v) >> 4) | LBO1;
+        const uint32_t sfq_lo = (sbase + L::sfq) >> 4, sfk_lo = (sbase + L::sfk) >> 4;
+        const uint32_t sfv_lo = (sbase + L::sfv) >> 4, sfp_lo = (sbase + L::sfp) >> 4;
+        const uint32_t a1_lo = ((sbase + L::a1) >> 4) | (((uint32_t)(L::zero - L::a1) >> 4) << 16);
+        const uint32_t b1_lo = ((sbase + L::b1) >> 4) | (((uint32_t)(L::zero - L::b1) >> 4) << 16);
+        const int n0t = n_t[0], n1t = n_t[1];
         bool ok = true;
-        int pv_cnt[2] = {0, 0}, pv_total = 0;
-        bool q_ready[2] = {false, false};
-        auto active = [&](int t, int it) { return (n_max - 1 - it) < n_t[t]; };
-        // S_t = delta_s + Q_t K^T for iteration `it` (K stage must be resident)
-        auto issue_qk = [&](int t, int it, bool first_of_it) -> bool {
-          const int s = it % kStages;
-          if (!q_ready[t]) {
+        uint32_t pv_cnt[2] = {0, 0}, pv_total = 0, q_done = 0;
+
+        // S_t = delta_s + Q_t K^T against K stage s (stage resident, tensor-memory proxy fenced)
+        auto issue_qk = [&](const int t, const int s, const bool first_of_it) -> bool {
+          if (!(q_done & (1u << t))) {
             if (!wait_bar(bars + Bars::q_full + 8 * t, 0, abort_s, P.status, 20)) return false;
-            q_ready[t] = true;
+            q_done |= 1u << t;
             tc_fence_after();
 #pragma unroll
-            for (int kb = 0; kb < kKB; ++kb)
-              tc_cp_sf(tm_sfq + 8 * t + 4 * kb, make_smem_desc(sbase + L::sfq + t * 1024 + kb * 512, 128, 0, 0));
+            for (int kb = 0; kb < kKB; ++kb) tc_cp_sf(tm_sfq + 8 * t + 4 * kb, sfq_lo + t * 64 + kb * 32, HI_SF);
           }
           if (first_of_it) {
 #pragma unroll
-            for (int kb = 0; kb < kKB; ++kb)
-              tc_cp_sf(tm_sfk + 4 * kb, make_smem_desc(sbase + L::sfk + s * 1024 + kb * 512, 128, 0, 0));
+            for (int kb = 0; kb < kKB; ++kb) tc_cp_sf(tm_sfk + 4 * kb, sfk_lo + s * 64 + kb * 32, HI_SF);
           }
           const uint32_t tm_S = tmem + 128 * t;
           if (has_ds) {
-            const uint32_t a1 = sbase + L::a1, b1 = sbase + L::b1 + (s * 2 + t) * 2048, z = sbase + L::zero;
-            tc_mma_bf16(tm_S, make_smem_desc(a1, 128, z - a1, 0), make_smem_desc(b1, 128, z - b1, 0), idesc_r1, 0);
+            // buffer i sits i*2048 bytes higher, so its distance to the shared zero chunk is i*2048 smaller
+            const uint32_t i = (uint32_t)(s * 2 + t);
+            tc_mma_bf16(tm_S, a1_lo, HI_SF, b1_lo + i * 128u - ((i * 128u) << 16), HI_SF, idesc_r1, 0);
           }
 #pragma unroll
-          for (int kb = 0; kb < kKB; ++kb) {
-            const uint64_t da = make_smem_desc(sbase + L::q + t * L::kQBytes + kb * 32, kSboQK, 16, kSwzQK);
-            const uint64_t db = make_smem_desc(sbase + L::k + s * L::kKBytes + kb * 32, kSboQK, 16, kSwzQK);
-            tc_mma_nvf4(tm_S, da, db, idesc_qk, tm_sfq + 8 * t + 4 * kb, tm_sfk + 4 * kb, (has_ds || kb > 0) ? 1u : 0u);
-          }
+          for (int kb = 0; kb < kKB; ++kb)
+            tc_mma_nvf4(tm_S, q_lo + t * (L::kQBytes >> 4) + kb * 2, HI_QK, k_lo + s * (L::kKBytes >> 4) + kb * 2, HI_QK,
+                        idesc_qk, tm_sfq + 8 * t + 4 * kb, tm_sfk + 4 * kb, (has_ds || kb > 0) ? 1u : 0u);
           tc_commit(bars + Bars::s_full + 8 * t);
           return true;
         };
-        auto wait_k = [&](int it) -> bool {
+        auto wait_k = [&](const int it) -> bool {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           if (!wait_bar(bars + Bars::k_full + 8 * s, ph, abort_s, P.status, 21)) return false;
@@ -353,55 +460,62 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         // prologue: scores of the first key tile
         ok = wait_k(0);
         {
-          bool first = true;
-          for (int t = 0; ok && t < 2; ++t)
-            if (active(t, 0)) { ok = issue_qk(t, 0, first); first = false; }
+          const bool a0 = (n_max - 1) < n0t, a1 = (n_max - 1) < n1t;
+          if (ok && a0) ok = issue_qk(0, 0, true);
+          if (ok && a1) ok = issue_qk(1, 0, !a0);
           if (ok) tc_commit(bars + Bars::k_empty);
         }
+        int s = 0, s_next = 1 % kStages;
+        uint32_t ph = 0;
         for (int it = 0; ok && it < n_max; ++it) {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
+          const int j = n_max - 1 - it;
           const bool more = it + 1 < n_max;
+          const bool act1 = j < n1t, act1n = (j - 1) < n1t;
           bool v_ready = false, k_next_ready = false;
-          for (int t = 0; ok && t < 2; ++t) {
-            if (active(t, it)) {
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            const bool act = t == 0 ? (j < n0t) : act1, actn = t == 0 ? ((j - 1) < n0t) : act1n;
+            // the warpgroup of tile t has consumed S_t and written P_t (nothing to wait for on the
+            // tile's first iteration)
+            if (ok && act) ok = wait_bar(bars + Bars::p_full + 8 * t, pv_cnt[t] & 1, abort_s, P.status, 23);
+            if (ok && more && actn) {
+              // S_t of the next key tile goes first: the softmax chain is waiting for it, whereas the
+              // P.V product below is only folded in afterwards
+              if (!k_next_ready) ok = wait_k(it + 1);
+              if (ok) ok = issue_qk(t, s_next, !k_next_ready);
+              k_next_ready = true;
+              if (ok && (t == 1 || !act1n)) tc_commit(bars + Bars::k_empty + 8 * s_next);
+            }
+            if (ok && act) {
               // O_tile = P_t V
-              if (!(ok = wait_bar(bars + Bars::p_full + 8 * t, pv_cnt[t] & 1, abort_s, P.status, 23))) break;
               if (!v_ready) {
-                if (!(ok = wait_bar(bars + Bars::v_full + 8 * s, ph, abort_s, P.status, 24))) break;
+                ok = wait_bar(bars + Bars::v_full + 8 * s, ph, abort_s, P.status, 24);
                 v_ready = true;
+                if (ok) {
+                  tc_fence_after();
+#pragma unroll
+                  for (int kb = 0; kb < 2; ++kb) tc_cp_sf(tm_sfv + 4 * kb, sfv_lo + s * 64 + kb * 32, HI_SF);
+                }
+              }
+              if (ok && pv_total > 0) ok = wait_bar(bars + Bars::o_free, (pv_total - 1) & 1, abort_s, P.status, 22);
+              if (ok) {
                 tc_fence_after();
 #pragma unroll
+                for (int kb = 0; kb < 2; ++kb) tc_cp_sf(tm_sfp + 8 * t + 4 * kb, sfp_lo + t * 64 + kb * 32, HI_SF);
+#pragma unroll
                 for (int kb = 0; kb < 2; ++kb)
-                  tc_cp_sf(tm_sfv + 4 * kb, make_smem_desc(sbase + L::sfv + s * 1024 + kb * 512, 128, 0, 0));
+                  tc_mma_nvf4(tm_O, p_lo + t * (L::kPBytes >> 4) + kb * 2, HI_PV, v_lo + s * (L::kVBytes >> 4) + kb * 2, HI_PV,
+                              idesc_pv, tm_sfp + 8 * t + 4 * kb, tm_sfv + 4 * kb, kb > 0);
+                tc_commit(bars + Bars::o_full + 8 * t);
+                ++pv_cnt[t];
+                ++pv_total;
+                if (t == 1 || !act1) tc_commit(bars + Bars::v_empty + 8 * s);   // last PV of this stage
               }
-              if (pv_total > 0 && !(ok = wait_bar(bars + Bars::o_free, (pv_total - 1) & 1, abort_s, P.status, 22))) break;
-              tc_fence_after();
-#pragma unroll
-              for (int kb = 0; kb < 2; ++kb)
-                tc_cp_sf(tm_sfp + 8 * t + 4 * kb, make_smem_desc(sbase + L::sfp + t * 1024 + kb * 512, 128, 0, 0));
-#pragma unroll
-              for (int kb = 0; kb < 2; ++kb) {
-                const uint64_t da = make_smem_desc(sbase + L::p + t * L::kPBytes + kb * 32, 512, 16, 4);
-                const uint64_t db = make_smem_desc(sbase + L::v + s * L::kVBytes + kb * 32, 512, 16, 4);
-                tc_mma_nvf4(tm_O, da, db, idesc_pv, tm_sfp + 8 * t + 4 * kb, tm_sfv + 4 * kb, kb > 0);
-              }
-              tc_commit(bars + Bars::o_full + 8 * t);
-              ++pv_cnt[t];
-              ++pv_total;
-              if (t == 1 || !active(1, it)) tc_commit(bars + Bars::v_empty + 8 * s);   // last PV of this stage
-            }
-            if (more && active(t, it + 1)) {
-              // S_t of the next key tile; S_t is free: its softmax warpgroup has signalled p_full
-              // for this iteration above (or this is the tile's first iteration)
-              if (!k_next_ready) {
-                if (!(ok = wait_k(it + 1))) break;
-              }
-              if (!(ok = issue_qk(t, it + 1, !k_next_ready))) break;
-              k_next_ready = true;
-              if (t == 1 || !active(1, it + 1)) tc_commit(bars + Bars::k_empty + 8 * ((it + 1) % kStages));
             }
           }
+          s = s_next;
+          s_next = (s_next + 1 == kStages) ? 0 : s_next + 1;
+          if (s == 0) ph ^= 1;
         }
         if (!ok) {
           // giving up: let every MMA / scale copy already issued finish before tensor memory is freed
@@ -410,8 +524,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         }
       }
     } else {
-      // ------------------------------------------------------------------ softmax + O accumulation
-      asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+      // ------------------------------------------------------------------ exp / quantise + O accumulation
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
       const int t = warp >> 2;                                   // query tile of this warpgroup
       const int row = threadIdx.x & 127;                         // tensor-memory lane
       const int n_mine = n_t[t];
@@ -420,16 +534,15 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       if (n_mine > 0) {
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t tm_S = tmem + 128 * t + lane_addr;
-        const int causal_lim = kCausal ? qpos + P.Nk - P.Nq : 0x7fffffff;   // last visible key
-        const int key_lim = min(P.Nk - 1, causal_lim);
+        const int key_lim = min(P.Nk - 1, kCausal ? qpos + P.Nk - P.Nq : 0x7fffffff);   // last visible key
         const float c = P.scale_log2;
-        const float2 c2 = make_float2(c, c);
         float2 O2[D / 2];
 #pragma unroll
         for (int i = 0; i < D / 2; ++i) O2[i] = make_float2(0.f, 0.f);
         float m = -INFINITY, l = 0.f;                            // m in raw score units
         uint8_t* p_row = smem + L::p + t * L::kPBytes + row * 64;
         const int swz = (row >> 1) & 3;
+        float2* st = reinterpret_cast<float2*>(smem + L::stats) + t * 8 * 128 + row;
         uint32_t* sfp_row = reinterpret_cast<uint32_t*>(smem + L::sfp + t * 1024 + sf_atom_offset(row, 0));
         const uint32_t bar_s = bars + Bars::s_full + 8 * t, bar_p = bars + Bars::p_full + 8 * t;
         const uint32_t bar_o = bars + Bars::o_full + 8 * t;
@@ -442,85 +555,36 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           if (!(ok = wait_bar(bar_s, it & 1, abort_s, P.status, 30))) break;
           tc_fence_after();
 
-          // ---- pass 1: per-16-key block maxima of the raw scores
-          float bm[8];
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            uint32_t r[32];
-            tmem_ld32(tm_S + ch * 32, r);
-            tmem_wait_ld();
-            if (need_mask) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (n0 + ch * 32 + i > key_lim) r[i] = 0xff800000u;
-            }
-            bm[ch * 2 + 0] = max16(r);
-            bm[ch * 2 + 1] = max16(r + 16);
-          }
-          const float m_new = fmaxf(fmax3(fmax3(bm[0], bm[1], bm[2]), fmax3(bm[3], bm[4], bm[5]), fmax3(bm[6], bm[7], m)), m);
-          const float m_fin = (m_new == -INFINITY) ? 0.f : m_new;
-          const float alpha = ex2_approx((m - m_fin) * c);          // 0 on the first tile
-          const float off = fmaf(m_fin, c, kLog2Inv2688);           // P = 2^(s*c - off) in (0, 2688]
-          m = m_new;
-          // per-block scale (P blockmax / 6), stored as E4M3 for the PV MMA
-          float sb[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) sb[i] = ex2_approx(fmaf(bm[i], c, kLog2Inv6) - off);
-          sfp_row[0] = f32x2_to_e4m3x2(sb[0], sb[1]) | (f32x2_to_e4m3x2(sb[2], sb[3]) << 16);
-          sfp_row[128] = f32x2_to_e4m3x2(sb[4], sb[5]) | (f32x2_to_e4m3x2(sb[6], sb[7]) << 16);
-
-          // ---- pass 2, one 16-key block at a time: P / scale = 2^(s*c - (bm*c + log2(1/6))) in [0, 6]
-          // -> E2M1; the row sum uses the unrounded values times the unrounded block scale
-          float lsum = 0.f;
-          uint32_t code[4];
-#pragma unroll
-          for (int blk = 0; blk < 8; ++blk) {
-            uint32_t r[16];
-            tmem_ld16(tm_S + blk * 16, r);
-            tmem_wait_ld();
-            if (need_mask) {
-#pragma unroll
-              for (int i = 0; i < 16; ++i)
-                if (n0 + blk * 16 + i > key_lim) r[i] = 0xff800000u;
-            }
-            const float nb = (bm[blk] == -INFINITY) ? 0.f : -fmaf(bm[blk], c, kLog2Inv6);
-            const float2 nb2 = make_float2(nb, nb);
-            float2 e[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              e[i] = ffma2(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), c2, nb2);
-              e[i].x = ex2_approx(e[i].x);
-              e[i].y = ex2_approx(e[i].y);
-            }
-            const float2 s4 = fadd2(fadd2(fadd2(e[0], e[1]), fadd2(e[2], e[3])), fadd2(fadd2(e[4], e[5]), fadd2(e[6], e[7])));
-            lsum = fmaf(s4.x + s4.y, sb[blk], lsum);
-            code[(blk & 1) * 2 + 0] = f32x8_to_e2m1x8(e[0].x, e[0].y, e[1].x, e[1].y, e[2].x, e[2].y, e[3].x, e[3].y);
-            code[(blk & 1) * 2 + 1] = f32x8_to_e2m1x8(e[4].x, e[4].y, e[5].x, e[5].y, e[6].x, e[6].y, e[7].x, e[7].y);
-            if (blk & 1)
-              *reinterpret_cast<uint4*>(p_row + (((blk >> 1) ^ swz) << 4)) = make_uint4(code[0], code[1], code[2], code[3]);
-          }
-          l = fmaf(l, alpha, lsum);
+          const float alpha = need_mask ? softmax_tile_masked(tm_S, c, m, l, st, sfp_row, p_row, swz, n0, key_lim)
+                                        : softmax_tile_plain(tm_S, c, m, l, st, sfp_row, p_row, swz);
           // S consumed and P^ written: hand both to the MMA warp
           tc_fence_before();
           fence_proxy_async_smem();
           mbar_arrive(bar_p);
 
-          // ---- O = O * alpha + P^ V^
+          // ---- O = O * alpha + P^ V^ (loads again one 16-column chunk ahead)
           if (!(ok = wait_bar(bar_o, it & 1, abort_s, P.status, 31))) break;
           tc_fence_after();
           const float2 al2 = make_float2(alpha, alpha);
+          uint32_t ra[16], rb[16];
+          tmem_ld16(tm_O + lane_addr, ra);
 #pragma unroll
-          for (int ch = 0; ch < D / 32; ++ch) {
-            uint32_t r[32];
-            tmem_ld32(tm_O + lane_addr + ch * 32, r);
+          for (int ch = 0; ch < D / 16; ch += 2) {
             tmem_wait_ld();
-            if (ch == D / 32 - 1) {          // product is in registers: the other tile's PV may overwrite it
+            tmem_ld16(tm_O + lane_addr + (ch + 1) * 16, rb);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              O2[ch * 8 + i] = ffma2(O2[ch * 8 + i], al2, make_float2(__uint_as_float(ra[2 * i]), __uint_as_float(ra[2 * i + 1])));
+            tmem_wait_ld();
+            if (ch + 2 < D / 16) {
+              tmem_ld16(tm_O + lane_addr + (ch + 2) * 16, ra);
+            } else {                          // the product is in registers: the other tile's PV may overwrite it
               tc_fence_before();
               mbar_arrive(bars + Bars::o_free);
             }
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-              O2[ch * 16 + i] = ffma2(O2[ch * 16 + i], al2, make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])));
+            for (int i = 0; i < 8; ++i)
+              O2[(ch + 1) * 8 + i] = ffma2(O2[(ch + 1) * 8 + i], al2, make_float2(__uint_as_float(rb[2 * i]), __uint_as_float(rb[2 * i + 1])));
           }
         }
 
