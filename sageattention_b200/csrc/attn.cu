@@ -23,11 +23,11 @@
 //               softmax arithmetic while the other waits for its MMAs
 //   warp  8     TMA producer (Q tiles once, then a ring of K and V stages; scale factors and the
 //               delta_s rows by plain bulk copies)
-//   warp  9     MMA issuer (one lane): tcgen05.cp of scale factors, QK and PV MMAs for both tiles
+//   warp  9     QK issuer (one lane): scale-factor copies, rank-1 delta_s MMA and Q.K^T MMAs, both tiles
 //   warp 10     turns each delta_s row (128 bf16) into the B operand of a rank-1 bf16 MMA
 //               (ones x delta_s) that initialises the score accumulator, so the softmax warps never
 //               touch delta_s
-//   warp 11     idle (completes the warpgroup that hands its registers to the softmax warps)
+//   warp 11     PV issuer (one lane): scale-factor copies and P.V MMAs for both tiles
 //
 // Tensor memory (512 columns): S0 [0,128) S1 [128,256) PV product [256,256+D) (shared by both
 // tiles, drained into registers right after each PV MMA) and 48 columns of scale factors.
@@ -88,8 +88,8 @@ struct Bars {            // byte offsets inside the barrier block
   static constexpr int p_full = s_full + 16;              // [2]
   static constexpr int o_full = p_full + 16;              // [2]
   static constexpr int o_free = o_full + 16;
-  static constexpr int drain = o_free + 8;                // MMA warp's last commit when giving up
-  static constexpr int tmem_slot = drain + 8;             // u32 written by tcgen05.alloc
+  static constexpr int drain = o_free + 8;                // [2] the issuers' last commit when giving up
+  static constexpr int tmem_slot = drain + 16;             // u32 written by tcgen05.alloc
   static constexpr int abort_flag = tmem_slot + 8;
   static constexpr int run_flag = abort_flag + 4;
 };
@@ -145,17 +145,16 @@ __device__ __forceinline__ float max16(const uint32_t* r) {
   return fmaxf(fmax3(a, b, c), fmax3(d, e, __uint_as_float(r[15])));
 }
 
-// One key tile for one score row (one thread): pass 1 finds the 16-key block maxima, pass 2 turns the
-// scores into E2M1 codes of P / blockscale and the row sum.  Straight-line code (no branch when kMask
-// is false) so that the scheduler can overlap the exp2 stream of one block with the adds and
-// conversions of its neighbour; every tensor-memory load is issued one block before its use.
+// One key tile for one score row (one thread), in two passes over tensor memory.  Straight-line code
+// (no branch when kMask is false) so that the scheduler can overlap the exp2 stream of one block with
+// the adds and conversions of its neighbour; every load is issued one 16-key block before its use.
 //   m, l      running row maximum (raw score units) and row sum (of P = 2^(s*c - m*c) * 2688)
 //   st        this thread's column of the shared scratch: per block (exponent offset, scale)
-//   returns   alpha = 2^((m_old - m_new) * c), the factor the O row must be rescaled by
+// Pass 1: block maxima -> new row maximum, rescale factor alpha = 2^((m_old - m_new) * c) (returned),
+// per-block scales (P blockmax / 6) as E4M3 bytes for the PV MMA (`sfp`) and, unrounded, in `st`.
 template <bool kMask>
-__device__ __forceinline__ float softmax_tile_impl(const uint32_t tm_S, const float c, float& m, float& l, float2* st,
-                                              uint32_t* sfp_row, uint8_t* p_row, const int swz, const int n0,
-                                              const int key_lim) {
+__device__ __forceinline__ float softmax_pass1_impl(const uint32_t tm_S, const float c, float& m, float2* st,
+                                                    uint2& sfp, const int n0, const int key_lim) {
   uint32_t ra[16], rb[16];
   float bm[8];
   tmem_ld16(tm_S, ra);
@@ -169,7 +168,7 @@ __device__ __forceinline__ float softmax_tile_impl(const uint32_t tm_S, const fl
     }
     bm[blk] = max16(ra);
     tmem_wait_ld();
-    tmem_ld16(tm_S + ((blk + 2) & 7) * 16, ra);          // the last one already fetches block 0 for pass 2
+    if (blk + 2 < 8) tmem_ld16(tm_S + (blk + 2) * 16, ra);
     if (kMask) {
 #pragma unroll
       for (int i = 0; i < 16; ++i) rb[i] = (n0 + (blk + 1) * 16 + i > key_lim) ? 0xff800000u : rb[i];
@@ -181,23 +180,29 @@ __device__ __forceinline__ float softmax_tile_impl(const uint32_t tm_S, const fl
   const float alpha = ex2_approx((m - m_fin) * c);          // 0 on the first tile
   const float off = fmaf(m_fin, c, kLog2Inv2688);           // P = 2^(s*c - off) in (0, 2688]
   m = m_new;
-  // per block: exponent offset that yields P / scale directly, and the scale (P blockmax / 6); parked
-  // in this thread's own shared-memory column to keep registers for the O row
-  {
-    float sb[8];
+  float sb[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float e = fmaf(bm[i], c, kLog2Inv6);
-      sb[i] = ex2_approx(e - off);
-      st[i * 128] = make_float2((bm[i] == -INFINITY) ? 0.f : -e, sb[i]);
-    }
-    sfp_row[0] = f32x2_to_e4m3x2(sb[0], sb[1]) | (f32x2_to_e4m3x2(sb[2], sb[3]) << 16);
-    sfp_row[128] = f32x2_to_e4m3x2(sb[4], sb[5]) | (f32x2_to_e4m3x2(sb[6], sb[7]) << 16);
+  for (int i = 0; i < 8; ++i) {
+    const float e = fmaf(bm[i], c, kLog2Inv6);
+    sb[i] = ex2_approx(e - off);
+    st[i * 128] = make_float2((bm[i] == -INFINITY) ? 0.f : -e, sb[i]);
   }
-  // ---- pass 2
+  sfp.x = f32x2_to_e4m3x2(sb[0], sb[1]) | (f32x2_to_e4m3x2(sb[2], sb[3]) << 16);   // keys 0-63 of the tile
+  sfp.y = f32x2_to_e4m3x2(sb[4], sb[5]) | (f32x2_to_e4m3x2(sb[6], sb[7]) << 16);   // keys 64-127
+  return alpha;
+}
+
+// Pass 2: P / blockscale = 2^(s*c - (bm*c + log2(1/6))) in [0, 6] -> E2M1 codes into the swizzled P^ tile;
+// the row sum uses the unrounded values times the unrounded block scale (softmax_fused.h:135-153).
+template <bool kMask>
+__device__ __forceinline__ void softmax_pass2_impl(const uint32_t tm_S, const float c, const float alpha, float& l,
+                                                   const float2* st, uint8_t* p_row, const int swz, const int n0,
+                                                   const int key_lim) {
+  uint32_t ra[16], rb[16];
   const float2 c2 = make_float2(c, c);
   float lsum = 0.f;
   uint32_t code[4];
+  tmem_ld16(tm_S, ra);
   float2 ns = st[0];
 #pragma unroll
   for (int blk = 0; blk < 8; ++blk) {
@@ -226,20 +231,18 @@ __device__ __forceinline__ float softmax_tile_impl(const uint32_t tm_S, const fl
     ns = ns_next;
   }
   l = fmaf(l, alpha, lsum);
-  return alpha;
 }
 
-// The unmasked tile is the hot path and is inlined; tiles that need the key-padding / causal mask are
-// rare (the last key tile, the diagonal) and go through a real call so that their extra selects do not
-// cost the hot path registers.
-__device__ __forceinline__ float softmax_tile_plain(const uint32_t tm_S, const float c, float& m, float& l, float2* st,
-                                                    uint32_t* sfp_row, uint8_t* p_row, const int swz) {
-  return softmax_tile_impl<false>(tm_S, c, m, l, st, sfp_row, p_row, swz, 0, 0);
+// Tiles that need the key-padding / causal mask are rare (the last key tile, the diagonal) and go
+// through real calls so that their extra selects do not cost the hot path registers.
+__device__ __noinline__ float softmax_pass1_masked(const uint32_t tm_S, const float c, float& m, float2* st,
+                                                   uint2& sfp, const int n0, const int key_lim) {
+  return softmax_pass1_impl<true>(tm_S, c, m, st, sfp, n0, key_lim);
 }
-__device__ __noinline__ float softmax_tile_masked(const uint32_t tm_S, const float c, float& m, float& l, float2* st,
-                                                  uint32_t* sfp_row, uint8_t* p_row, const int swz, const int n0,
+__device__ __noinline__ void softmax_pass2_masked(const uint32_t tm_S, const float c, const float alpha, float& l,
+                                                  const float2* st, uint8_t* p_row, const int swz, const int n0,
                                                   const int key_lim) {
-  return softmax_tile_impl<true>(tm_S, c, m, l, st, sfp_row, p_row, swz, n0, key_lim);
+  softmax_pass2_impl<true>(tm_S, c, alpha, l, st, p_row, swz, n0, key_lim);
 }
 
 template <int D, bool kCausal>
@@ -301,6 +304,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
     }
     mbar_init(bars + Bars::o_free, 128);
     mbar_init(bars + Bars::drain, 1);
+    mbar_init(bars + Bars::drain + 8, 1);
     // a failure reported by an earlier CTA (or an earlier launch that shares *status) stops new work
     const int bad = *reinterpret_cast<volatile int*>(P.status) != 0;
     *abort_s = bad;
@@ -402,26 +406,22 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           if (lane == 0) mbar_arrive(bars + Bars::ds_ready + 8 * s);
         }
       } else if (warp == 9 && lane == 0) {
-        // ---------------------------------------------------------------- MMA issuer
+        // ---------------------------------------------------------------- QK issuer
         // This one thread paces the whole CTA, so its instruction stream is kept minimal: every
         // shared-memory descriptor is a constant high word (stride / swizzle / version bits) plus a
         // low word (address >> 4, leading-offset field) that only needs an integer add per use.
         constexpr uint32_t idesc_qk = make_idesc_nvf4(kBlockM, kBlockN);
-        constexpr uint32_t idesc_pv = make_idesc_nvf4(kBlockM, D);
         constexpr uint32_t idesc_r1 = make_idesc_bf16(kBlockM, kBlockN);
         constexpr uint32_t HI_QK = (kSboQK >> 4) | (1u << 14) | (kSwzQK << 29);
-        constexpr uint32_t HI_PV = (512u >> 4) | (1u << 14) | (4u << 29);
         constexpr uint32_t HI_SF = (128u >> 4) | (1u << 14);          // 8x16-byte core matrices, no swizzle
         constexpr uint32_t LBO1 = 1u << 16;                            // leading offset field of swizzled operands
         const uint32_t q_lo = ((sbase + L::q) >> 4) | LBO1, k_lo = ((sbase + L::k) >> 4) | LBO1;
-        const uint32_t p_lo = ((sbase + L::p) >> 4) | LBO1, v_lo = ((sbase + L::v) >> 4) | LBO1;
         const uint32_t sfq_lo = (sbase + L::sfq) >> 4, sfk_lo = (sbase + L::sfk) >> 4;
-        const uint32_t sfv_lo = (sbase + L::sfv) >> 4, sfp_lo = (sbase + L::sfp) >> 4;
         const uint32_t a1_lo = ((sbase + L::a1) >> 4) | (((uint32_t)(L::zero - L::a1) >> 4) << 16);
         const uint32_t b1_lo = ((sbase + L::b1) >> 4) | (((uint32_t)(L::zero - L::b1) >> 4) << 16);
         const int n0t = n_t[0], n1t = n_t[1];
         bool ok = true;
-        uint32_t pv_cnt[2] = {0, 0}, pv_total = 0, q_done = 0;
+        uint32_t pv_cnt[2] = {0, 0}, q_done = 0;
 
         // S_t = delta_s + Q_t K^T against K stage s (stage resident, tensor-memory proxy fenced)
         auto issue_qk = [&](const int t, const int s, const bool first_of_it) -> bool {
@@ -465,62 +465,83 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           if (ok && a1) ok = issue_qk(1, 0, !a0);
           if (ok) tc_commit(bars + Bars::k_empty);
         }
-        int s = 0, s_next = 1 % kStages;
-        uint32_t ph = 0;
+        int s_next = 1 % kStages;
         for (int it = 0; ok && it < n_max; ++it) {
           const int j = n_max - 1 - it;
           const bool more = it + 1 < n_max;
-          const bool act1 = j < n1t, act1n = (j - 1) < n1t;
-          bool v_ready = false, k_next_ready = false;
+          const bool act1n = (j - 1) < n1t;
+          bool k_next_ready = false;
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
-            const bool act = t == 0 ? (j < n0t) : act1, actn = t == 0 ? ((j - 1) < n0t) : act1n;
-            // the warpgroup of tile t has consumed S_t and written P_t (nothing to wait for on the
-            // tile's first iteration)
-            if (ok && act) ok = wait_bar(bars + Bars::p_full + 8 * t, pv_cnt[t] & 1, abort_s, P.status, 23);
+            const bool act = t == 0 ? (j < n0t) : (j < n1t), actn = t == 0 ? ((j - 1) < n0t) : act1n;
+            // the warpgroup of tile t has consumed S_t (nothing to wait for on the tile's first iteration)
+            if (ok && act) {
+              ok = wait_bar(bars + Bars::p_full + 8 * t, pv_cnt[t] & 1, abort_s, P.status, 23);
+              ++pv_cnt[t];
+            }
             if (ok && more && actn) {
-              // S_t of the next key tile goes first: the softmax chain is waiting for it, whereas the
-              // P.V product below is only folded in afterwards
               if (!k_next_ready) ok = wait_k(it + 1);
               if (ok) ok = issue_qk(t, s_next, !k_next_ready);
               k_next_ready = true;
               if (ok && (t == 1 || !act1n)) tc_commit(bars + Bars::k_empty + 8 * s_next);
             }
-            if (ok && act) {
-              // O_tile = P_t V
-              if (!v_ready) {
-                ok = wait_bar(bars + Bars::v_full + 8 * s, ph, abort_s, P.status, 24);
-                v_ready = true;
-                if (ok) {
-                  tc_fence_after();
-#pragma unroll
-                  for (int kb = 0; kb < 2; ++kb) tc_cp_sf(tm_sfv + 4 * kb, sfv_lo + s * 64 + kb * 32, HI_SF);
-                }
-              }
-              if (ok && pv_total > 0) ok = wait_bar(bars + Bars::o_free, (pv_total - 1) & 1, abort_s, P.status, 22);
-              if (ok) {
-                tc_fence_after();
-#pragma unroll
-                for (int kb = 0; kb < 2; ++kb) tc_cp_sf(tm_sfp + 8 * t + 4 * kb, sfp_lo + t * 64 + kb * 32, HI_SF);
-#pragma unroll
-                for (int kb = 0; kb < 2; ++kb)
-                  tc_mma_nvf4(tm_O, p_lo + t * (L::kPBytes >> 4) + kb * 2, HI_PV, v_lo + s * (L::kVBytes >> 4) + kb * 2, HI_PV,
-                              idesc_pv, tm_sfp + 8 * t + 4 * kb, tm_sfv + 4 * kb, kb > 0);
-                tc_commit(bars + Bars::o_full + 8 * t);
-                ++pv_cnt[t];
-                ++pv_total;
-                if (t == 1 || !act1) tc_commit(bars + Bars::v_empty + 8 * s);   // last PV of this stage
-              }
-            }
           }
-          s = s_next;
           s_next = (s_next + 1 == kStages) ? 0 : s_next + 1;
-          if (s == 0) ph ^= 1;
         }
         if (!ok) {
           // giving up: let every MMA / scale copy already issued finish before tensor memory is freed
           tc_commit(bars + Bars::drain);
           mbar_wait(bars + Bars::drain, 0, 1u << 20);
+        }
+      } else if (warp == 11 && lane == 0) {
+        // ---------------------------------------------------------------- PV issuer
+        // O_tile = P_t V for both tiles, from its own thread so that waiting for the shared product
+        // buffer never delays the next QK.
+        constexpr uint32_t idesc_pv = make_idesc_nvf4(kBlockM, D);
+        constexpr uint32_t HI_PV = (512u >> 4) | (1u << 14) | (4u << 29);
+        constexpr uint32_t HI_SF = (128u >> 4) | (1u << 14);
+        constexpr uint32_t LBO1 = 1u << 16;
+        const uint32_t p_lo = ((sbase + L::p) >> 4) | LBO1, v_lo = ((sbase + L::v) >> 4) | LBO1;
+        const uint32_t sfv_lo = (sbase + L::sfv) >> 4, sfp_lo = (sbase + L::sfp) >> 4;
+        const int n0t = n_t[0], n1t = n_t[1];
+        bool ok = true;
+        uint32_t pv_cnt[2] = {0, 0}, pv_total = 0, ph = 0;
+        int s = 0;
+        for (int it = 0; ok && it < n_max; ++it) {
+          const int j = n_max - 1 - it;
+          const bool act1 = j < n1t;
+          bool v_ready = false;
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            const bool act = t == 0 ? (j < n0t) : act1;
+            if (!(ok && act)) continue;
+            if (!(ok = wait_bar(bars + Bars::p_full + 8 * t, pv_cnt[t] & 1, abort_s, P.status, 26))) break;
+            if (!v_ready) {
+              if (!(ok = wait_bar(bars + Bars::v_full + 8 * s, ph, abort_s, P.status, 24))) break;
+              v_ready = true;
+              tc_fence_after();
+#pragma unroll
+              for (int kb = 0; kb < 2; ++kb) tc_cp_sf(tm_sfv + 4 * kb, sfv_lo + s * 64 + kb * 32, HI_SF);
+            }
+            if (pv_total > 0 && !(ok = wait_bar(bars + Bars::o_free, (pv_total - 1) & 1, abort_s, P.status, 22))) break;
+            tc_fence_after();
+#pragma unroll
+            for (int kb = 0; kb < 2; ++kb) tc_cp_sf(tm_sfp + 8 * t + 4 * kb, sfp_lo + t * 64 + kb * 32, HI_SF);
+#pragma unroll
+            for (int kb = 0; kb < 2; ++kb)
+              tc_mma_nvf4(tm_O, p_lo + t * (L::kPBytes >> 4) + kb * 2, HI_PV, v_lo + s * (L::kVBytes >> 4) + kb * 2, HI_PV,
+                          idesc_pv, tm_sfp + 8 * t + 4 * kb, tm_sfv + 4 * kb, kb > 0);
+            tc_commit(bars + Bars::o_full + 8 * t);
+            ++pv_cnt[t];
+            ++pv_total;
+            if (t == 1 || !act1) tc_commit(bars + Bars::v_empty + 8 * s);   // last PV of this stage
+          }
+          s = (s + 1 == kStages) ? 0 : s + 1;
+          if (s == 0) ph ^= 1;
+        }
+        if (!ok) {
+          tc_commit(bars + Bars::drain + 8);
+          mbar_wait(bars + Bars::drain + 8, 0, 1u << 20);
         }
       }
     } else {
@@ -548,24 +569,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         const uint32_t bar_o = bars + Bars::o_full + 8 * t;
         bool ok = true;
 
-        for (int it = 0; it < n_mine; ++it) {
-          const int j = n_mine - 1 - it;
-          const int n0 = j * kBlockN;
-          const bool need_mask = (n0 + kBlockN - 1 >= P.Nk) || (kCausal && n0 + kBlockN - 1 > q0 + P.Nk - P.Nq);
-          if (!(ok = wait_bar(bar_s, it & 1, abort_s, P.status, 30))) break;
+        // O = O * alpha + (P^ V^ of one key tile), product read from tensor memory 16 columns at a time
+        // with the next load in flight; the shared product buffer is released as soon as it is in registers
+        auto fold_product = [&](const float alpha_) {
           tc_fence_after();
-
-          const float alpha = need_mask ? softmax_tile_masked(tm_S, c, m, l, st, sfp_row, p_row, swz, n0, key_lim)
-                                        : softmax_tile_plain(tm_S, c, m, l, st, sfp_row, p_row, swz);
-          // S consumed and P^ written: hand both to the MMA warp
-          tc_fence_before();
-          fence_proxy_async_smem();
-          mbar_arrive(bar_p);
-
-          // ---- O = O * alpha + P^ V^ (loads again one 16-column chunk ahead)
-          if (!(ok = wait_bar(bar_o, it & 1, abort_s, P.status, 31))) break;
-          tc_fence_after();
-          const float2 al2 = make_float2(alpha, alpha);
+          const float2 al2 = make_float2(alpha_, alpha_);
           uint32_t ra[16], rb[16];
           tmem_ld16(tm_O + lane_addr, ra);
 #pragma unroll
@@ -578,7 +586,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
             tmem_wait_ld();
             if (ch + 2 < D / 16) {
               tmem_ld16(tm_O + lane_addr + (ch + 2) * 16, ra);
-            } else {                          // the product is in registers: the other tile's PV may overwrite it
+            } else {
               tc_fence_before();
               mbar_arrive(bars + Bars::o_free);
             }
@@ -586,7 +594,35 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
             for (int i = 0; i < 8; ++i)
               O2[(ch + 1) * 8 + i] = ffma2(O2[(ch + 1) * 8 + i], al2, make_float2(__uint_as_float(rb[2 * i]), __uint_as_float(rb[2 * i + 1])));
           }
+        };
+
+        float alpha_prev = 0.f;
+        for (int it = 0; it < n_mine; ++it) {
+          const int j = n_mine - 1 - it;
+          const int n0 = j * kBlockN;
+          const bool need_mask = (n0 + kBlockN - 1 >= P.Nk) || (kCausal && n0 + kBlockN - 1 > q0 + P.Nk - P.Nq);
+          if (!(ok = wait_bar(bar_s, it & 1, abort_s, P.status, 30))) break;
+          tc_fence_after();
+          uint2 sfp;
+          const float alpha = need_mask ? softmax_pass1_masked(tm_S, c, m, st, sfp, n0, key_lim)
+                                        : softmax_pass1_impl<false>(tm_S, c, m, st, sfp, 0, 0);
+          // The PV MMA of the previous key tile has finished by now (it was issued while pass 1 ran):
+          // its product is folded into O here, and P^ / its scales may be overwritten from here on.
+          if (it > 0) {
+            if (!(ok = wait_bar(bar_o, (it - 1) & 1, abort_s, P.status, 31))) break;
+            fold_product(alpha_prev);
+          }
+          sfp_row[0] = sfp.x;
+          sfp_row[128] = sfp.y;
+          if (need_mask) softmax_pass2_masked(tm_S, c, alpha, l, st, p_row, swz, n0, key_lim);
+          else softmax_pass2_impl<false>(tm_S, c, alpha, l, st, p_row, swz, 0, 0);
+          alpha_prev = alpha;
+          // S consumed and P^ written: hand both to the MMA issuers
+          tc_fence_before();
+          fence_proxy_async_smem();
+          mbar_arrive(bar_p);
         }
+        if (ok && (ok = wait_bar(bar_o, (n_mine - 1) & 1, abort_s, P.status, 32))) fold_product(alpha_prev);
 
         // ---- epilogue: O / l -> bf16 -> global (row-contiguous 16-byte stores)
         if (ok && qpos < P.Nq) {
