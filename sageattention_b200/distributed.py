@@ -1,0 +1,185 @@
+"""Multi-GPU layer of the FP4 attention path: one process per GPU, ``torch.distributed`` (NCCL over
+NVLink / NVSwitch on the GPUs, gloo in the CPU tests).
+
+The reference has no communication code (its one multi-GPU example delegates to the external xDiT
+package, ``example/parallel_sageattn_cogvideo.py:8-14,89-95``, whose Ulysses degree must divide the
+head count, ``:31-36``).  Two schemes are provided:
+
+* **head sharding** - smoothing, quantisation and attention are independent per (batch, kv head), so
+  ranks take disjoint sets of (batch, kv-head group) units and nothing is exchanged on the data path
+  (:func:`shard_units`, :func:`sageattn_head_parallel`).
+* **Ulysses sequence parallelism** for sequences held sequence-sharded ``[B, N/P, H, D]``: one
+  all-to-all turns the sequence shards of all heads into all tokens of ``H/P`` heads, the single-GPU
+  operator runs unchanged (K means and Q block means see the whole sequence, so no further
+  collective is needed), and one all-to-all brings the output back (:func:`ulysses_attention`).
+  Heads are processed in chunks so that the exchange of chunk ``i+1`` overlaps the attention of
+  chunk ``i``.  Every exchanged tile lands in local HBM first; the kernels only ever read local
+  memory.
+"""
+from __future__ import annotations
+
+import os
+import time
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_units(batch: int, kv_heads: int, world_size: int) -> List[List[Tuple[int, int]]]:
+    """Split the ``batch x kv_heads`` independent units over ranks as evenly as possible, keeping
+    each rank's units contiguous (query heads follow their kv head, so GQA groups are never split)."""
+    units = [(b, h) for b in range(batch) for h in range(kv_heads)]
+    base, extra = divmod(len(units), world_size)
+    out, pos = [], 0
+    for r in range(world_size):
+        n = base + (1 if r < extra else 0)
+        out.append(units[pos:pos + n])
+        pos += n
+    return out
+
+
+def sageattn_head_parallel(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group=None, gather: bool = True,
+                           attn_fn: Optional[Callable] = None, **kwargs) -> torch.Tensor:
+    """Every rank holds the full HND tensors, computes the heads of its share of kv heads and
+    (optionally) all-gathers the outputs.  Requires ``Hkv % world_size == 0``."""
+    if attn_fn is None:
+        from .api import sageattn as attn_fn
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    B, Hq, N, D = q.shape
+    Hkv = k.shape[1]
+    if Hkv % world != 0:
+        raise ValueError("head sharding needs the number of kv heads to be a multiple of the world size")
+    hk = Hkv // world
+    g = Hq // Hkv
+    qs = q[:, rank * hk * g:(rank + 1) * hk * g]
+    ks, vs = k[:, rank * hk:(rank + 1) * hk], v[:, rank * hk:(rank + 1) * hk]
+    out = attn_fn(qs.contiguous(), ks.contiguous(), vs.contiguous(), tensor_layout="HND", **kwargs)
+    if not gather:
+        return out
+    parts = [torch.empty_like(out) for _ in range(world)]
+    dist.all_gather(parts, out.contiguous(), group=group)
+    return torch.cat(parts, dim=1)
+
+
+def _seq_to_head(x: torch.Tensor, world: int, group, async_op: bool = False):
+    """[B, n, H, D] sequence shard -> [B, world*n, H/world, D] (all tokens, this rank's heads)."""
+    B, n, H, D = x.shape
+    send = x.reshape(B, n, world, H // world, D).permute(2, 0, 1, 3, 4).contiguous()   # [P, B, n, h, D]
+    recv = torch.empty_like(send)
+    work = dist.all_to_all_single(recv, send, group=group, async_op=async_op)
+
+    def finish():
+        # recv[p] = tokens of rank p's sequence shard for my heads
+        return recv.permute(1, 0, 2, 3, 4).reshape(B, world * n, H // world, D)
+    return work, finish
+
+
+def _head_to_seq(x: torch.Tensor, world: int, group, async_op: bool = False):
+    """[B, world*n, h, D] (all tokens, my heads) -> [B, n, world*h, D] (my tokens, all heads)."""
+    B, N, h, D = x.shape
+    n = N // world
+    send = x.reshape(B, world, n, h, D).permute(1, 0, 2, 3, 4).contiguous()            # [P, B, n, h, D]
+    recv = torch.empty_like(send)
+    work = dist.all_to_all_single(recv, send, group=group, async_op=async_op)
+
+    def finish():
+        # recv[p] = my tokens for rank p's heads
+        return recv.permute(1, 2, 0, 3, 4).reshape(B, n, world * h, D)
+    return work, finish
+
+
+def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group=None, head_chunks: int = 1,
+                      attn_fn: Optional[Callable] = None, **kwargs) -> torch.Tensor:
+    """Sequence-parallel attention.  q, k, v: this rank's sequence shard ``[B, N/P, H, D]`` ("NHD";
+    shard r holds tokens ``r*N/P ... (r+1)*N/P - 1``).  Returns the output shard ``[B, N/P, H, D]``.
+
+    Requires ``H % (P * head_chunks) == 0`` and the same head count for q, k, v (expand GQA first).
+    With ``head_chunks > 1`` the all-to-all of the next chunk of heads is in flight while the current
+    chunk is attended.
+    """
+    if attn_fn is None:
+        from .api import sageattn as attn_fn
+    world = dist.get_world_size(group)
+    B, n, H, D = q.shape
+    if k.shape != q.shape or v.shape != q.shape:
+        raise ValueError("ulysses_attention expects q, k, v of identical shape [B, N/P, H, D]")
+    if H % (world * head_chunks) != 0:
+        raise ValueError(f"the head count {H} must be a multiple of world_size * head_chunks = {world * head_chunks}")
+    hc = H // head_chunks
+    outs = [None] * head_chunks
+
+    def launch(c):
+        sl = slice(c * hc, (c + 1) * hc)
+        return [_seq_to_head(t[:, :, sl], world, group, async_op=True) for t in (q, k, v)]
+
+    pending = launch(0)
+    back = []
+    for c in range(head_chunks):
+        cur = pending
+        if c + 1 < head_chunks:
+            pending = launch(c + 1)
+        full = []
+        for work, finish in cur:
+            work.wait()
+            full.append(finish())
+        o = attn_fn(full[0], full[1], full[2], tensor_layout="NHD", **kwargs)          # [B, N, hc/P, D]
+        back.append(_head_to_seq(o, world, group, async_op=True))
+    for c, (work, finish) in enumerate(back):
+        work.wait()
+        outs[c] = finish()                                                             # [B, n, hc, D] heads in rank order
+    if head_chunks == 1:
+        return outs[0]
+    # chunk c carried global heads [c*hc, (c+1)*hc): rank p's part of it sits at [p*hc/P, (p+1)*hc/P)
+    return torch.cat(outs, dim=2)
+
+
+# ----------------------------------------------------------------------------------------------------
+# benchmark leg used by bench.py --workload ulysses
+# ----------------------------------------------------------------------------------------------------
+
+def bench_ulysses(args, w, dist_mod, dev):
+    import json
+    import sageattention_b200 as sa
+    rank, world = dist_mod.get_rank(), dist_mod.get_world_size()
+    B, H, N, D = w["B"], w["Hq"], w["N"], w["D"]
+    if H % world or N % world:
+        raise SystemExit("ulysses workload: heads and tokens must be multiples of the number of GPUs")
+    n = N // world
+    g = torch.Generator(device=dev).manual_seed(4321 + rank)
+    q = torch.randn((B, n, H, D), generator=g, device=dev).to(torch.bfloat16)
+    koff = torch.randn((B, 1, H, D), generator=torch.Generator(device=dev).manual_seed(99), device=dev) * w["k_off"]
+    k = (torch.randn((B, n, H, D), generator=g, device=dev) + koff).to(torch.bfloat16)
+    v = torch.randn((B, n, H, D), generator=g, device=dev).to(torch.bfloat16)
+    chunks = 2 if (H // world) % 2 == 0 else 1
+
+    def step():
+        return ulysses_attention(q, k, v, head_chunks=chunks, is_causal=w["causal"])
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    dist_mod.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    dist_mod.barrier()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev, dtype=torch.float64)
+    dist_mod.all_reduce(t, op=dist_mod.ReduceOp.MAX)
+    ms = t.item()
+    flops = 4.0 * B * H * N * N * D / (2 if w["causal"] else 1)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "attention_tops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "fp4 (e2m1 x ue4m3 block-scaled, fp32 accumulate)",
+            "data": "synthetic",
+            "config": {"workload": "ulysses", "B": B, "H": H, "N": N, "D": D, "causal": w["causal"],
+                       "sharding": f"sequence-sharded input, all-to-all to {H // world} heads per GPU, {chunks} head chunk(s)",
+                       "step": "3 all-to-all + K mean + fused quant + delta_s + attention + 1 all-to-all"},
+            "gpu_launches": 4 * chunks * args.steps}), flush=True)
+    dist_mod.destroy_process_group()
