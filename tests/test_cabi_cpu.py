@@ -1,0 +1,80 @@
+"""The C-ABI library loads without a GPU and exports every function the header declares; argument
+checks that need no device are exercised through ctypes."""
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+
+from sageattention_b200 import _lib
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = ROOT / "include" / "sage3_b200.h"
+
+
+def declared_functions():
+    text = HEADER.read_text()
+    return re.findall(r"SAGE3_API\s+[\w\s\*]+?\b(sage3_\w+)\s*\(", text)
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    names = declared_functions()
+    assert len(names) >= 8
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in include/sage3_b200.h but not exported"
+    assert set(names) >= set(_lib.EXPORTS)
+
+
+def test_version_and_status_strings():
+    lib = _lib.load()
+    assert lib.sage3_version() >= 100
+    assert lib.sage3_status_string(0) == b"ok"
+    for code in (1, 2, 3, 4):
+        assert len(lib.sage3_status_string(code)) > 5
+    assert lib.sage3_status_string(99) == b"unknown status"
+
+
+def test_buffer_sizes_and_shape_checks():
+    lib = _lib.load()
+    z = _lib.Sizes()
+    s = _lib.Shape(1, 8, 8, 1024, 1024, 128)
+    assert lib.sage3_buffer_sizes(C.byref(s), 1, C.byref(z)) == _lib.OK
+    assert z.q_codes == 8 * 1024 * 64 and z.q_sf == 8 * 8 * 2 * 512
+    assert z.vt_codes == 8 * 8 * 128 * 64 and z.vt_sf == 8 * 8 * 1024
+    assert z.delta_s == 8 * 8 * 1024 * 2 and z.km == 8 * 128 * 2
+    assert z.workspace >= z.q_codes + z.k_codes + z.vt_codes + z.delta_s
+    # ragged lengths round up to whole 128-token tiles
+    s2 = _lib.Shape(2, 4, 2, 130, 1, 64)
+    assert lib.sage3_buffer_sizes(C.byref(s2), 1, C.byref(z)) == _lib.OK
+    assert z.q_codes == 2 * 4 * 2 * 128 * 32 and z.k_codes == 2 * 2 * 1 * 128 * 32
+    for bad in (_lib.Shape(1, 8, 8, 128, 128, 96), _lib.Shape(1, 3, 2, 128, 128, 128)):
+        assert lib.sage3_buffer_sizes(C.byref(bad), 1, C.byref(z)) == _lib.ERR_UNSUPPORTED
+    assert lib.sage3_buffer_sizes(C.byref(_lib.Shape(0, 1, 1, 1, 1, 128)), 1, C.byref(z)) == _lib.ERR_ARGUMENT
+    assert lib.sage3_buffer_sizes(None, 1, C.byref(z)) == _lib.ERR_ARGUMENT
+
+
+def test_null_and_misaligned_arguments_are_rejected_before_any_launch():
+    lib = _lib.load()
+    assert lib.sage3_quant_qkv(None, None) == _lib.ERR_ARGUMENT
+    assert lib.sage3_attn_fwd(None, None) == _lib.ERR_ARGUMENT
+    assert lib.sage3_attention(None, None) == _lib.ERR_ARGUMENT
+    a = _lib.QuantArgs()
+    a.shape = _lib.Shape(1, 1, 1, 128, 128, 128)
+    a.q = _lib.Tensor(0x1008, 128 * 128, 128 * 128, 128)       # not 16-byte aligned
+    assert lib.sage3_quant_qkv(C.byref(a), None) == _lib.ERR_ARGUMENT
+    a.q = _lib.Tensor(0x1000, 128 * 128, 128 * 128, 130)        # rows not 16-byte aligned
+    assert lib.sage3_quant_qkv(C.byref(a), None) == _lib.ERR_ARGUMENT
+    a.q = _lib.Tensor(0x1000, 128 * 128, 128 * 128, 128)        # outputs missing
+    assert lib.sage3_quant_qkv(C.byref(a), None) == _lib.ERR_ARGUMENT
+    t = _lib.AttnArgs()
+    t.shape = _lib.Shape(1, 1, 1, 128, 128, 128)
+    assert lib.sage3_attn_fwd(C.byref(t), None) == _lib.ERR_ARGUMENT
+
+
+def test_front_end_refuses_cpu_tensors():
+    import torch
+    import sageattention_b200 as sa
+    q = torch.zeros(1, 1, 128, 128, dtype=torch.bfloat16)
+    with pytest.raises(ValueError):
+        sa.sageattn(q, q, q)
