@@ -306,9 +306,9 @@ __global__ void __launch_bounds__(kThreads) quant_qkv_kernel(const QuantLaunch P
 // host side
 // ------------------------------------------------------------------------------------------------
 static int pick_chunk_tokens(int N, int BH) {
-  // enough CTAs to fill 148 SMs twice, but at most 64 partial rows per (b,h)
+  // enough CTAs (8 per SM on 148 SMs) to keep the memory system full, but at most 64 partial rows per (b,h)
   int chunk = 4096;
-  while (chunk > 512 && (int64_t)BH * ((N + chunk - 1) / chunk) < 296) chunk >>= 1;
+  while (chunk > 256 && (int64_t)BH * ((N + chunk - 1) / chunk) < 1184) chunk >>= 1;
   while ((N + chunk - 1) / chunk > 64) chunk <<= 1;
   return chunk;
 }
