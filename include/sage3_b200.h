@@ -44,8 +44,9 @@ enum {
   SAGE3_ERR_ARGUMENT = 1,     /* null pointer, bad size, bad stride, buffer too small            */
   SAGE3_ERR_UNSUPPORTED = 2,  /* head_dim not in {64,128}, Hq not a multiple of Hkv, ...          */
   SAGE3_ERR_CUDA = 3,         /* a CUDA runtime / driver call failed (see sage3_last_cuda_error)  */
-  SAGE3_ERR_DEVICE_WAIT = 4   /* a bounded wait inside a kernel gave up (read back via
+  SAGE3_ERR_DEVICE_WAIT = 4,  /* a bounded wait inside a kernel gave up (read back via
                                  sage3_read_device_status)                                        */
+  SAGE3_ERR_TOO_LARGE = 5     /* problem exceeds the fixed scratch of sage3_k_mean_static         */
 };
 
 typedef struct {
@@ -136,6 +137,24 @@ SAGE3_API int sage3_buffer_sizes(const sage3_shape* shape, int per_block_mean, s
 SAGE3_API int sage3_quant_qkv(const sage3_quant_args* args, void* stream);
 SAGE3_API int sage3_attn_fwd(const sage3_attn_args* args, void* stream);
 SAGE3_API int sage3_attention(const sage3_fwd_args* args, void* stream);
+
+/* K channel means (bf16 [B,Hkv,D] into km_out; shape->Hq and shape->Nq are ignored) for callers that
+ * cannot allocate device memory where they run - for example a server that gave all device memory to
+ * its own pool at start-up, or a hook in which cudaMalloc's device-wide synchronisation or its failure
+ * under memory pressure cannot be tolerated.  It has no counterpart in the reference.  The result is
+ * the one sage3_quant_qkv writes to `km`; the reduction scratch is a fixed array inside the library
+ * (about 1 MiB per GPU, held until the process exits) instead of a caller buffer, and the function
+ * calls neither cudaMalloc nor cudaFree nor any other allocating routine.
+ *   limit      B*Hkv*chunks <= 2048 partial rows and B*Hkv <= 2048, where chunks = ceil(Nk / c) and the
+ *              chunk length c is a power of two of at least 256 tokens chosen so that each head has at
+ *              most 64 chunks; e.g. B=1 Hkv=40 Nk=32760 uses 40*32 = 1280 rows.  Larger problems
+ *              return SAGE3_ERR_TOO_LARGE.
+ *   set-up     the first call made with a given device current looks up the array's address on that
+ *              device (cudaGetSymbolAddress); make that first call before any stream capture.
+ *   sharing    all calls on a device use the same array, which keeps the previous call's contents;
+ *              the function zeroes the counters it needs on `stream` first.  Two calls whose kernels
+ *              can overlap on the GPU (different streams, no ordering between them) race on it. */
+SAGE3_API int sage3_k_mean_static(const sage3_shape* shape, const sage3_tensor* k, void* km_out, void* stream);
 
 /* Synchronises `stream`, copies the device status word back and maps it to a status
  * (SAGE3_OK or SAGE3_ERR_DEVICE_WAIT); *code_out, if given, receives the raw word. */

@@ -11,7 +11,7 @@ from pathlib import Path
 _HERE = Path(__file__).resolve().parent
 LIB_PATH = _HERE / "libsage3_b200.so"
 
-OK, ERR_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE_WAIT = range(5)
+OK, ERR_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE_WAIT, ERR_TOO_LARGE = range(6)
 
 
 class Shape(C.Structure):
@@ -60,7 +60,8 @@ class FwdArgs(C.Structure):
 
 
 EXPORTS = ("sage3_version", "sage3_status_string", "sage3_last_cuda_error", "sage3_buffer_sizes",
-           "sage3_quant_qkv", "sage3_attn_fwd", "sage3_attention", "sage3_read_device_status")
+           "sage3_quant_qkv", "sage3_attn_fwd", "sage3_attention", "sage3_read_device_status",
+           "sage3_k_mean_static")
 
 _lib = None
 
@@ -83,6 +84,7 @@ def load() -> C.CDLL:
     lib.sage3_attn_fwd.argtypes = [C.POINTER(AttnArgs), C.c_void_p]
     lib.sage3_attention.argtypes = [C.POINTER(FwdArgs), C.c_void_p]
     lib.sage3_read_device_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
+    lib.sage3_k_mean_static.argtypes = [C.POINTER(Shape), C.POINTER(Tensor), C.c_void_p, C.c_void_p]
     for name in EXPORTS:
         getattr(lib, name)            # raises AttributeError if an export is missing
     _lib = lib

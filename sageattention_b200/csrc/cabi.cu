@@ -51,6 +51,7 @@ const char* sage3_status_string(int status) {
     case SAGE3_ERR_UNSUPPORTED: return "unsupported shape (head_dim must be 64 or 128, Hq a multiple of Hkv)";
     case SAGE3_ERR_CUDA: return "CUDA call failed (see sage3_last_cuda_error)";
     case SAGE3_ERR_DEVICE_WAIT: return "a bounded wait inside a kernel gave up";
+    case SAGE3_ERR_TOO_LARGE: return "problem exceeds the fixed scratch of sage3_k_mean_static (2048 partial rows / 2048 heads)";
     default: return "unknown status";
   }
 }
@@ -204,6 +205,21 @@ int sage3_attention(const sage3_fwd_args* a, void* stream) {
   t.out = a->out; t.out_stride_b = a->out_stride_b; t.out_stride_h = a->out_stride_h; t.out_stride_n = a->out_stride_n;
   t.lse = a->lse; t.sm_scale = sm_scale; t.is_causal = a->is_causal; t.device_status = status;
   return sage3_attn_fwd(&t, stream);
+}
+
+int sage3_k_mean_static(const sage3_shape* shape, const sage3_tensor* k, void* km_out, void* stream) {
+  if (shape == nullptr || k == nullptr || k->ptr == nullptr || km_out == nullptr) return SAGE3_ERR_ARGUMENT;
+  if (shape->B <= 0 || shape->Hkv <= 0 || shape->Nk <= 0) return SAGE3_ERR_ARGUMENT;
+  if (shape->D != 64 && shape->D != 128) return SAGE3_ERR_UNSUPPORTED;
+  if (int st = check_tensor(*k)) return st;
+  if (!aligned16(km_out)) return SAGE3_ERR_ARGUMENT;
+  bool too_large = false;
+  cudaError_t e = sage3::launch_channel_mean_static(k->ptr, k->stride_b, k->stride_h, k->stride_n, shape->B, shape->Hkv,
+                                                    shape->Nk, shape->D, (float)shape->Nk, km_out, (cudaStream_t)stream,
+                                                    &too_large);
+  if (too_large) return SAGE3_ERR_TOO_LARGE;
+  if (e != cudaSuccess) return cuda_fail(e);
+  return SAGE3_OK;
 }
 
 int sage3_read_device_status(const int32_t* device_status, void* stream, int32_t* code_out) {

@@ -21,6 +21,8 @@ size_t quant_scratch_bytes(int B, int H, int N, int D);
 cudaError_t launch_channel_mean(const void* x, int64_t sb, int64_t sh, int64_t sn, int B, int H, int N, int D,
                                 float divisor, void* scratch, void* mean_out, cudaStream_t stream);
 cudaError_t launch_quant_qkv(const QuantArgs& a, cudaStream_t stream);
+cudaError_t launch_channel_mean_static(const void* x, int64_t sb, int64_t sh, int64_t sn, int B, int H, int N, int D,
+                                       float divisor, void* mean_out, cudaStream_t stream, bool* too_large);
 
 struct DeltaSArgs {
   const void* qm;                         // bf16 [B,Hq,Tq,D]

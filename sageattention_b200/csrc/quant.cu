@@ -367,4 +367,59 @@ cudaError_t launch_quant_qkv(const QuantArgs& a, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
+// ------------------------------------------------------------------------------------------------
+// Channel means with the reduction scratch inside the library.
+//
+// Some hosts of this library may not call cudaMalloc at the point where they need the K means: an
+// inference server that handed all device memory to its own pool at start-up, or a plug-in hook that
+// runs where an allocation (which synchronises the device and can fail under memory pressure) is not
+// acceptable.  For them the partial sums and arrival counters of channel_mean_kernel live in the
+// fixed array below instead of a caller buffer.  Every GPU that loads the library holds the array
+// (1 MiB + 8 KiB) until the process exits.
+//
+// In host code `g_static_scratch` is only a handle for the symbol, not a device address; the address
+// on the current device comes from cudaGetSymbolAddress, once per device, on the first call made
+// with that device current.
+// ------------------------------------------------------------------------------------------------
+constexpr int kStaticMaxRows = 2048;                                   // partial rows: B * H * chunks
+constexpr int kStaticMaxHeads = 2048;                                  // arrival counters: B * H
+constexpr size_t kStaticPartialBytes = (size_t)kStaticMaxRows * 128 * sizeof(float);
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticPartialBytes + kStaticMaxHeads * sizeof(unsigned int)];
+
+cudaError_t launch_channel_mean_static(const void* x, int64_t sb, int64_t sh, int64_t sn, int B, int H, int N, int D,
+                                       float divisor, void* mean_out, cudaStream_t stream, bool* too_large) {
+  *too_large = false;
+  const int chunk = pick_chunk_tokens(N, B * H);
+  const int nchunks = (N + chunk - 1) / chunk;
+  if ((int64_t)B * H * nchunks > kStaticMaxRows || (int64_t)B * H > kStaticMaxHeads) {
+    *too_large = true;
+    return cudaSuccess;
+  }
+  static void* base_of_device[64] = {};                                // device ordinal -> address of the array there
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  void* base = __atomic_load_n(&base_of_device[dev], __ATOMIC_ACQUIRE);
+  if (base == nullptr) {
+    e = cudaGetSymbolAddress(&base, g_static_scratch);
+    if (e != cudaSuccess) return e;
+    __atomic_store_n(&base_of_device[dev], base, __ATOMIC_RELEASE);    // same value whoever stores first
+  }
+  float* partial = reinterpret_cast<float*>(base);
+  unsigned int* counters = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(base) + kStaticPartialBytes);
+  // The array keeps whatever the previous call left.  Partial rows are fully overwritten before they
+  // are read; only the arrival counters must start at zero.
+  e = cudaMemsetAsync(counters, 0, (size_t)B * H * sizeof(unsigned int), stream);
+  if (e != cudaSuccess) return e;
+  dim3 grid(nchunks, B * H);
+  if (D == 128)
+    channel_mean_kernel<128><<<grid, kThreads, 0, stream>>>((const __nv_bfloat16*)x, sb, sh, sn, H, N, chunk, divisor,
+                                                            partial, counters, (__nv_bfloat16*)mean_out);
+  else
+    channel_mean_kernel<64><<<grid, kThreads, 0, stream>>>((const __nv_bfloat16*)x, sb, sh, sn, H, N, chunk, divisor,
+                                                           partial, counters, (__nv_bfloat16*)mean_out);
+  return cudaGetLastError();
+}
+
 }  // namespace sage3
