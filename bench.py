@@ -155,6 +155,44 @@ def run_reference_arm(args, w, name):
 
 
 # --------------------------------------------------------------------------------------------------
+# kernel sweep (the reference's bench/bench_baseline.py:9-11,30-31 shape: B=4, H=32)
+# --------------------------------------------------------------------------------------------------
+
+def run_sweep(args):
+    import sageattention_b200 as sa
+    dev = torch.device("cuda", 0)
+    for D in (128, 64):
+        for causal in (False, True):
+            for N in (1024, 2048, 4096, 8192, 16384, 32768):
+                w = dict(B=4, Hq=32, Hkv=32, N=N, D=D, causal=causal, k_off=0.0, v_out=0.0)
+                q, k, v = gen_inputs(w, 1000 + N, dev)
+                z = sa.quantize_qkv(q, k, v)
+                for _ in range(8):
+                    sa.fp4_attention(z, is_causal=causal)
+                ts = []
+                for _ in range(8):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    sa.fp4_attention(z, is_causal=causal)
+                    e1.record()
+                    torch.cuda.synchronize()
+                    ts.append(e0.elapsed_time(e1))
+                ms = sorted(ts)[len(ts) // 2]
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(4):
+                    sa.sageattn(q, k, v, is_causal=causal)
+                e1.record()
+                torch.cuda.synchronize()
+                ms_full = e0.elapsed_time(e1) / 4
+                fl = attn_flops(4, 32, N, N, D, causal)
+                print(json.dumps({"sweep": True, "D": D, "causal": causal, "N": N, "kernel_ms": ms,
+                                  "kernel_tops": fl / ms / 1e9, "operator_ms": ms_full,
+                                  "operator_tops": fl / ms_full / 1e9}), flush=True)
+                del q, k, v, z
+
+
+# --------------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------------
 
@@ -166,10 +204,14 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="dit", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sweep", action="store_true",
+                    help="kernel-only TOPS over B=4 H=32, D in {64,128}, N = 1K..32K, causal and not (one JSON line per point)")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     if args.impl == "reference":
         return run_reference_arm(args, w, args.workload)
+    if args.sweep:
+        return run_sweep(args)
     args.warmup = max(args.warmup, 3)
 
     import sageattention_b200 as sa
@@ -236,9 +278,8 @@ def main():
     oh = torch.empty_like(qh).pin_memory()
 
     def step_e2e():
-        qd, kd, vd = (x.to(dev, non_blocking=True) for x in (qh, kh, vh))
-        o = sa.sageattn(qd, kd, vd, tensor_layout="HND", is_causal=causal)
-        oh.copy_(o, non_blocking=True)
+        # host tensors in, host tensor out; copies of one head group overlap the kernels of another
+        sa.sageattn_from_host(qh, kh, vh, out=oh, device=dev, is_causal=causal)
 
     for _ in range(2):
         step_e2e()

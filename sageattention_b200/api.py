@@ -277,3 +277,65 @@ def sageattn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlen
                                  sm_scale=sm_scale, smooth_k=smooth_k, **kwargs)
         out[cq[i]:cq[i + 1]] = oi[0]
     return out
+
+
+_host_streams = {}
+
+
+def sageattn_from_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[torch.Tensor] = None,
+                       device=None, head_chunks: int = 8, is_causal: bool = False, sm_scale: Optional[float] = None,
+                       **kwargs) -> torch.Tensor:
+    """Attention on HOST tensors (HND ``[B,H,N,D]`` bf16, ideally pinned): the heads are processed in
+    ``head_chunks`` groups of kv heads, and the host-to-device copy of group ``i+1`` and the
+    device-to-host copy of group ``i-1`` run on their own streams while group ``i`` is computed, so the
+    PCIe transfers hide behind the kernels (or the other way round).  Returns the output as a host tensor
+    (``out`` if given, else a new pinned tensor).  The work is ordered after the caller's current stream
+    and the current stream waits for the last copy, so CUDA events recorded around the call time all of it;
+    the host must still synchronise before reading ``out``."""
+    if q.is_cuda or k.is_cuda or v.is_cuda:
+        raise ValueError("sageattn_from_host takes host tensors; use sageattn for device tensors")
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    B, Hq, Nq, D = q.shape
+    Hkv = k.shape[1]
+    if Hq % Hkv != 0:
+        raise ValueError("num_qo_heads must be a multiple of num_kv_heads")
+    g = Hq // Hkv
+    if out is None:
+        out = torch.empty_like(q).pin_memory()
+    chunks = max(1, min(head_chunks, Hkv))
+    bounds = [(Hkv * c) // chunks for c in range(chunks + 1)]
+    if dev not in _host_streams:
+        _host_streams[dev] = (torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev))
+    s_in, s_run, s_out = _host_streams[dev]
+    cur = torch.cuda.current_stream(dev)
+    start = torch.cuda.Event()
+    start.record(cur)
+    s_in.wait_event(start)
+    keep = []
+    for c in range(chunks):
+        h0, h1 = bounds[c], bounds[c + 1]
+        if h0 == h1:
+            continue
+        with torch.cuda.stream(s_in):
+            qd = q[:, h0 * g:h1 * g].to(dev, non_blocking=True)
+            kd = k[:, h0:h1].to(dev, non_blocking=True)
+            vd = v[:, h0:h1].to(dev, non_blocking=True)
+            ev_in = torch.cuda.Event()
+            ev_in.record(s_in)
+        with torch.cuda.stream(s_run):
+            s_run.wait_event(ev_in)
+            od = sageattn3_blackwell(qd, kd, vd, tensor_layout="HND", is_causal=is_causal, sm_scale=sm_scale, **kwargs)
+            ev_run = torch.cuda.Event()
+            ev_run.record(s_run)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_run)
+            out[:, h0 * g:h1 * g].copy_(od, non_blocking=True)
+        keep.append((qd, kd, vd, od))
+    done = torch.cuda.Event()
+    done.record(s_out)
+    cur.wait_event(done)
+    # the device buffers were allocated on side streams: tell the allocator the current stream orders their reuse
+    for tensors in keep:
+        for t in tensors:
+            t.record_stream(cur)
+    return out

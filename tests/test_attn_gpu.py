@@ -169,3 +169,12 @@ def test_full_size_properties():
     cos, l1 = sage3.accuracy(merged.cpu(), base.float().cpu())
     assert cos > 0.96, (cos, l1)
     assert (lm - lse).abs().max() < 0.05
+
+
+def test_host_tensor_entry_point_matches_device_operator():
+    q, k, v = U.make_qkv(2, 8, 4, 300, 300, 128, seed=12)
+    want = sa.sageattn(q.cuda(), k.cuda(), v.cuda(), is_causal=True).cpu()
+    for chunks in (1, 3, 8):
+        got = sa.sageattn_from_host(q.pin_memory(), k.pin_memory(), v.pin_memory(), head_chunks=chunks, is_causal=True)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want), chunks
