@@ -510,19 +510,16 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         for (int it = 0; ok && it < n_max; ++it) {
           const int j = n_max - 1 - it;
           const bool act1 = j < n1t;
-          bool v_ready = false;
+          // the V stage and its scale factors do not depend on the softmax: fetch them before waiting for P
+          if (!(ok = wait_bar(bars + Bars::v_full + 8 * s, ph, abort_s, P.status, 24))) break;
+          tc_fence_after();
+#pragma unroll
+          for (int kb = 0; kb < 2; ++kb) tc_cp_sf(tm_sfv + 4 * kb, sfv_lo + s * 64 + kb * 32, HI_SF);
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
             const bool act = t == 0 ? (j < n0t) : act1;
             if (!(ok && act)) continue;
             if (!(ok = wait_bar(bars + Bars::p_full + 8 * t, pv_cnt[t] & 1, abort_s, P.status, 26))) break;
-            if (!v_ready) {
-              if (!(ok = wait_bar(bars + Bars::v_full + 8 * s, ph, abort_s, P.status, 24))) break;
-              v_ready = true;
-              tc_fence_after();
-#pragma unroll
-              for (int kb = 0; kb < 2; ++kb) tc_cp_sf(tm_sfv + 4 * kb, sfv_lo + s * 64 + kb * 32, HI_SF);
-            }
             if (pv_total > 0 && !(ok = wait_bar(bars + Bars::o_free, (pv_total - 1) & 1, abort_s, P.status, 22))) break;
             tc_fence_after();
 #pragma unroll
@@ -596,7 +593,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           }
         };
 
-        float alpha_prev = 0.f;
         for (int it = 0; it < n_mine; ++it) {
           const int j = n_mine - 1 - it;
           const int n0 = j * kBlockN;
@@ -606,23 +602,20 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           uint2 sfp;
           const float alpha = need_mask ? softmax_pass1_masked(tm_S, c, m, st, sfp, n0, key_lim)
                                         : softmax_pass1_impl<false>(tm_S, c, m, st, sfp, 0, 0);
-          // The PV MMA of the previous key tile has finished by now (it was issued while pass 1 ran):
-          // its product is folded into O here, and P^ / its scales may be overwritten from here on.
-          if (it > 0) {
-            if (!(ok = wait_bar(bar_o, (it - 1) & 1, abort_s, P.status, 31))) break;
-            fold_product(alpha_prev);
-          }
           sfp_row[0] = sfp.x;
           sfp_row[128] = sfp.y;
           if (need_mask) softmax_pass2_masked(tm_S, c, alpha, l, st, p_row, swz, n0, key_lim);
           else softmax_pass2_impl<false>(tm_S, c, alpha, l, st, p_row, swz, 0, 0);
-          alpha_prev = alpha;
           // S consumed and P^ written: hand both to the MMA issuers
           tc_fence_before();
           fence_proxy_async_smem();
           mbar_arrive(bar_p);
+          // While the QK MMA of the next key tile is issued and runs, the P.V product of this one
+          // (issued by the other issuer thread at the same time) is folded into O.  Its completion
+          // also means P^ and its scales may be overwritten by the next iteration.
+          if (!(ok = wait_bar(bar_o, it & 1, abort_s, P.status, 31))) break;
+          fold_product(alpha);
         }
-        if (ok && (ok = wait_bar(bar_o, (n_mine - 1) & 1, abort_s, P.status, 32))) fold_product(alpha_prev);
 
         // ---- epilogue: O / l -> bf16 -> global (row-contiguous 16-byte stores)
         if (ok && qpos < P.Nq) {
