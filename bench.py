@@ -77,7 +77,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -319,7 +319,10 @@ def main():
         "kernel_only": {"attention_ms": attn_ms, "attention_tops": achieved, "preprocess_ms": quant_ms,
                         "preprocess_gbs": quant_bytes / (quant_ms * 1e-3) / 1e9},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_fp4, "unit": "TFLOP/s",
-                     "frac": achieved / peak_fp4, "traffic": None,
+                     "frac": achieved / peak_fp4,
+                     # ncu, quarter-size capture (profiles/attn_fwd_kernel_quarter_dit.md): 30.05 MB of DRAM traffic per
+                     # head at N = 32760, D = 128, proportional to the number of heads
+                     "traffic": (B * Hq * 30.05e6) if (N == 32760 and D == 128 and not causal) else None,
                      "note": f"peak = 4 x {which} sustained bf16 cuBLAS ({bf16_sus} TF/s): dense FP4 is 4x dense bf16 on "
                              f"B200; vs bf16 sustained itself: {achieved / bf16_sus:.3f}"},
         "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
