@@ -13,15 +13,17 @@
 //   O /= l, bf16                                      softmax_fused.h:156-173, fwd_epilogue.cu:103-147
 // Key tiles are visited from the last to the first as the reference does (fwd_mainloop.cu:575).
 //
-// One CTA per SM works on TWO adjacent 128-row query tiles of one head, which share every K / V
-// tile.  12 warps:
+// One persistent CTA per SM walks a static list of work items (CTA i takes items i, i + grid, ...);
+// an item is TWO adjacent 128-row query tiles of one head, which share every K / V tile.  All
+// barrier phases keep counting across items, so the loads and the first Q.K^T of the next item are
+// under way while the last softmax, fold and output store of the current one finish.  12 warps:
 //   warps 0-3   softmax warpgroup of query tile 0: thread r owns score row r (tensor-memory lane r)
 //               and the O row in registers.  Per key tile: pass 1 scans S for the 16-key block
 //               maxima, pass 2 turns S into P^; every tensor-memory load is issued one block ahead
 //               of its use; then the P.V product is folded into O.
 //   warps 4-7   the same for query tile 1; the two warpgroups run half a period apart, so one does
 //               softmax arithmetic while the other waits for its MMAs
-//   warp  8     TMA producer (Q tiles once, then a ring of K and V stages; scale factors and the
+//   warp  8     TMA producer (Q tiles per item, then a ring of K and V stages; scale factors and the
 //               delta_s rows by plain bulk copies)
 //   warp  9     QK issuer (one lane): scale-factor copies, rank-1 delta_s MMA and Q.K^T MMAs, both tiles
 //   warp 10     turns each delta_s row (128 bf16) into the B operand of a rank-1 bf16 MMA
@@ -79,7 +81,8 @@ struct Smem {
 
 struct Bars {            // byte offsets inside the barrier block
   static constexpr int q_full = 0;                        // [2]
-  static constexpr int k_full = 16;                       // [kStages]
+  static constexpr int q_empty = 16;                      // [2]
+  static constexpr int k_full = 32;                       // [kStages]
   static constexpr int k_empty = k_full + 8 * kStages;
   static constexpr int v_full = k_empty + 8 * kStages;
   static constexpr int v_empty = v_full + 8 * kStages;
@@ -245,6 +248,41 @@ __device__ __noinline__ void softmax_pass2_masked(const uint32_t tm_S, const flo
   softmax_pass2_impl<true>(tm_S, c, alpha, l, st, p_row, swz, n0, key_lim);
 }
 
+// One unit of work of a CTA: two adjacent query tiles of one head.
+struct Work {
+  int b, hq, hkv, pair;
+  int n_t[2];            // key tiles each query tile visits (0: none / tile does not exist)
+  int n_max;
+};
+
+template <bool kCausal>
+__device__ __forceinline__ Work get_work(const KParams& P, const int w) {
+  Work k;
+  const int n_pairs = (P.Tq + 1) >> 1;
+  // pairs of one head are adjacent in the work list (they share K/V in L2); the longest causal pairs first
+  k.pair = n_pairs - 1 - (w % n_pairs);
+  const int bh = w / n_pairs;
+  k.b = bh / P.Hq;
+  k.hq = bh % P.Hq;
+  k.hkv = k.hq / (P.Hq / P.Hkv);
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int qt = 2 * k.pair + t;
+    int n = 0;
+    if (qt < P.Tq) {
+      n = P.Tk;
+      if (kCausal) {
+        const int q_end = min((qt + 1) * kBlockM, P.Nq);
+        const int lim = q_end + P.Nk - P.Nq;               // keys [0, lim) can be visible
+        n = lim <= 0 ? 0 : min(P.Tk, (lim + kBlockN - 1) / kBlockN);
+      }
+    }
+    k.n_t[t] = n;
+  }
+  k.n_max = max(k.n_t[0], k.n_t[1]);
+  return k;
+}
+
 template <int D, bool kCausal>
 __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                                                                    const __grid_constant__ CUtensorMap tm_k,
@@ -260,47 +298,23 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
   const uint32_t bars = sbase + L::bars;
   volatile int* abort_s = reinterpret_cast<volatile int*>(smem + L::bars + Bars::abort_flag);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  // CTA -> (batch, head, pair of query tiles).  Pairs of one head are adjacent in the grid (they
-  // share K/V in L2); the longest causal pairs start first.
-  const int n_pairs = (P.Tq + 1) >> 1;
-  const int bid = blockIdx.x;
-  const int pair = n_pairs - 1 - (bid % n_pairs);
-  const int bh = bid / n_pairs, b = bh / P.Hq, hq = bh % P.Hq;
-  const int hkv = hq / (P.Hq / P.Hkv);
   const bool has_ds = P.ds != nullptr;
-
-  int n_t[2];            // key tiles each query tile visits (0: none / tile does not exist)
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const int qt = 2 * pair + t;
-    int n = 0;
-    if (qt < P.Tq) {
-      n = P.Tk;
-      if (kCausal) {
-        const int q_end = min((qt + 1) * kBlockM, P.Nq);
-        const int lim = q_end + P.Nk - P.Nq;               // keys [0, lim) can be visible
-        n = lim <= 0 ? 0 : min(P.Tk, (lim + kBlockN - 1) / kBlockN);
-      }
-    }
-    n_t[t] = n;
-  }
-  const int n_max = max(n_t[0], n_t[1]);
+  const int total_work = P.B * P.Hq * ((P.Tq + 1) >> 1);
 
   if (threadIdx.x == 0) {
-    mbar_init(bars + Bars::q_full, 1);
-    mbar_init(bars + Bars::q_full + 8, 1);
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(bars + Bars::q_full + 8 * t, 1);
+      mbar_init(bars + Bars::q_empty + 8 * t, 1);          // tcgen05.commit after the last QK that reads the tile
+      mbar_init(bars + Bars::s_full + 8 * t, 1);
+      mbar_init(bars + Bars::p_full + 8 * t, 128);
+      mbar_init(bars + Bars::o_full + 8 * t, 1);
+    }
     for (int s = 0; s < kStages; ++s) {
       mbar_init(bars + Bars::k_full + 8 * s, 1);
       mbar_init(bars + Bars::k_empty + 8 * s, 1);          // tcgen05.commit
       mbar_init(bars + Bars::v_full + 8 * s, 1);
       mbar_init(bars + Bars::v_empty + 8 * s, 1);          // tcgen05.commit
       mbar_init(bars + Bars::ds_ready + 8 * s, 1);
-    }
-    for (int t = 0; t < 2; ++t) {
-      mbar_init(bars + Bars::s_full + 8 * t, 1);
-      mbar_init(bars + Bars::p_full + 8 * t, 128);
-      mbar_init(bars + Bars::o_full + 8 * t, 1);
     }
     mbar_init(bars + Bars::o_free, 128);
     mbar_init(bars + Bars::drain, 1);
@@ -333,83 +347,100 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
   // read once after the barrier: every warp takes the same branch, so the register hand-over
   // below (setmaxnreg) is always executed by whole warpgroups
   const bool run = *reinterpret_cast<volatile int*>(smem + L::bars + Bars::run_flag) != 0;
-  if (n_max > 0 && run) {
+  // The CTA is persistent: every role walks the same static list of work items (blockIdx.x, +gridDim.x, ...)
+  // and all barrier phases simply keep counting across items, so the loads, MMAs and softmax of the
+  // next item start while the tail of the current one is still being finished.
+  if (run) {
     if (warp >= 8) {
       asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
       if (warp == 8 && lane == 0) {
         // ---------------------------------------------------------------- TMA producer
         prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
-        int64_t ds_row[2];
+        uint32_t g = 0;                       // K/V stages completely issued so far
+        uint32_t gk = 0;                      // K stages issued so far (g or g + 1)
+        uint32_t qn[2] = {0, 0};              // Q tiles loaded so far per slot
+        bool ok = true;
+        for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+          const Work wk = get_work<kCausal>(P, w);
+          int64_t ds_row[2];
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          const int qt = 2 * pair + t;
-          ds_row[t] = ((int64_t)b * P.Hq + hq) * P.ds_rows + (P.ds_rows == 1 ? 0 : qt);
-          if (n_t[t] > 0) {
-            const int64_t qtile = ((int64_t)b * P.Hq + hq) * P.Tq + qt;
-            const uint32_t qb = bars + Bars::q_full + 8 * t;
-            mbar_arrive_expect_tx(qb, L::kQBytes + L::kSfRow);
-            tma_load_2d(sbase + L::q + t * L::kQBytes, &tm_q, 0, (int)(qtile * kBlockM), qb);
-            bulk_load(sbase + L::sfq + t * 1024, P.q_sf + qtile * L::kSfRow, L::kSfRow, qb);
+          for (int t = 0; t < 2; ++t) {
+            const int qt = 2 * wk.pair + t;
+            ds_row[t] = ((int64_t)wk.b * P.Hq + wk.hq) * P.ds_rows + (P.ds_rows == 1 ? 0 : qt);
+            if (ok && wk.n_t[t] > 0) {
+              // the slot's previous Q tile must have been read by its last QK MMA
+              if (qn[t] > 0 && !(ok = wait_bar(bars + Bars::q_empty + 8 * t, (qn[t] - 1) & 1, abort_s, P.status, 12))) break;
+              const int64_t qtile = ((int64_t)wk.b * P.Hq + wk.hq) * P.Tq + qt;
+              const uint32_t qb = bars + Bars::q_full + 8 * t;
+              mbar_arrive_expect_tx(qb, L::kQBytes + L::kSfRow);
+              tma_load_2d(sbase + L::q + t * L::kQBytes, &tm_q, 0, (int)(qtile * kBlockM), qb);
+              bulk_load(sbase + L::sfq + t * 1024, P.q_sf + qtile * L::kSfRow, L::kSfRow, qb);
+              ++qn[t];
+            }
           }
-        }
-        const int64_t kvhead = ((int64_t)b * P.Hkv + hkv) * P.Tk;
-        int issued = 0;
-        for (int it = 0; it < n_max; ++it) {
-          const int j = n_max - 1 - it, s = it % kStages;
-          const uint32_t ph = ((it / kStages) & 1) ^ 1;
-          if (!wait_bar(bars + Bars::k_empty + 8 * s, ph, abort_s, P.status, 10)) break;
-          const uint32_t kb = bars + Bars::k_full + 8 * s;
-          const int nds = has_ds ? (int)(j < n_t[0]) + (int)(j < n_t[1]) : 0;
-          mbar_arrive_expect_tx(kb, L::kKBytes + L::kSfRow + 256 * nds);
-          tma_load_2d(sbase + L::k + s * L::kKBytes, &tm_k, 0, (int)((kvhead + j) * kBlockN), kb);
-          bulk_load(sbase + L::sfk + s * 1024, P.k_sf + (kvhead + j) * L::kSfRow, L::kSfRow, kb);
-          if (has_ds) {
+          const int64_t kvhead = ((int64_t)wk.b * P.Hkv + wk.hkv) * P.Tk;
+          for (int it = 0; ok && it < wk.n_max; ++it, ++g) {
+            const int j = wk.n_max - 1 - it, s = g % kStages;
+            const uint32_t ph = ((g / kStages) & 1) ^ 1;
+            if (!(ok = wait_bar(bars + Bars::k_empty + 8 * s, ph, abort_s, P.status, 10))) break;
+            const uint32_t kb = bars + Bars::k_full + 8 * s;
+            const int nds = has_ds ? (int)(j < wk.n_t[0]) + (int)(j < wk.n_t[1]) : 0;
+            mbar_arrive_expect_tx(kb, L::kKBytes + L::kSfRow + 256 * nds);
+            tma_load_2d(sbase + L::k + s * L::kKBytes, &tm_k, 0, (int)((kvhead + j) * kBlockN), kb);
+            bulk_load(sbase + L::sfk + s * 1024, P.k_sf + (kvhead + j) * L::kSfRow, L::kSfRow, kb);
+            if (has_ds) {
 #pragma unroll
-            for (int t = 0; t < 2; ++t)
-              if (j < n_t[t])
-                bulk_load(sbase + L::dsraw + (s * 2 + t) * 256, P.ds + (ds_row[t] * P.Tk + j) * kBlockN, 256, kb);
+              for (int t = 0; t < 2; ++t)
+                if (j < wk.n_t[t])
+                  bulk_load(sbase + L::dsraw + (s * 2 + t) * 256, P.ds + (ds_row[t] * P.Tk + j) * kBlockN, 256, kb);
+            }
+            ++gk;
+            if (!(ok = wait_bar(bars + Bars::v_empty + 8 * s, ph, abort_s, P.status, 11))) break;
+            const uint32_t vb = bars + Bars::v_full + 8 * s;
+            mbar_arrive_expect_tx(vb, L::kVBytes + L::kSfV);
+            tma_load_2d(sbase + L::v + s * L::kVBytes, &tm_v, 0, (int)((kvhead + j) * D), vb);
+            bulk_load(sbase + L::sfv + s * 1024, P.vt_sf + (kvhead + j) * L::kSfV, L::kSfV, vb);
           }
-          if (!wait_bar(bars + Bars::v_empty + 8 * s, ph, abort_s, P.status, 11)) break;
-          const uint32_t vb = bars + Bars::v_full + 8 * s;
-          mbar_arrive_expect_tx(vb, L::kVBytes + L::kSfV);
-          tma_load_2d(sbase + L::v + s * L::kVBytes, &tm_v, 0, (int)((kvhead + j) * D), vb);
-          bulk_load(sbase + L::sfv + s * 1024, P.vt_sf + (kvhead + j) * L::kSfV, L::kSfV, vb);
-          ++issued;
         }
         if (*abort_s) {
           // giving up: the copies this thread started must land before the CTA may exit
           for (int t = 0; t < 2; ++t)
-            if (n_t[t] > 0) mbar_wait(bars + Bars::q_full + 8 * t, 0, 1u << 20);
-          for (int it = max(0, issued - kStages); it < issued; ++it) {
-            mbar_wait(bars + Bars::k_full + 8 * (it % kStages), (it / kStages) & 1, 1u << 20);
-            mbar_wait(bars + Bars::v_full + 8 * (it % kStages), (it / kStages) & 1, 1u << 20);
-          }
+            if (qn[t] > 0) mbar_wait(bars + Bars::q_full + 8 * t, (qn[t] - 1) & 1, 1u << 20);
+          for (uint32_t i = (gk > (uint32_t)kStages ? gk - kStages : 0); i < gk; ++i)
+            mbar_wait(bars + Bars::k_full + 8 * (i % kStages), (i / kStages) & 1, 1u << 20);
+          for (uint32_t i = (g > (uint32_t)kStages ? g - kStages : 0); i < g; ++i)
+            mbar_wait(bars + Bars::v_full + 8 * (i % kStages), (i / kStages) & 1, 1u << 20);
         }
       } else if (warp == 10 && has_ds) {
         // ---------------------------------------------------------------- delta_s -> rank-1 B operand
         // B1 is a K-major [128 keys x 16] bf16 operand in 8x16-byte core matrices: key n's first
         // element sits at (n/8)*128 + (n%8)*16; everything else stays zero.
-        for (int it = 0; it < n_max; ++it) {
-          const int j = n_max - 1 - it, s = it % kStages;
-          if (!wait_bar(bars + Bars::k_full + 8 * s, (it / kStages) & 1, abort_s, P.status, 40)) break;
+        uint32_t g = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+          const Work wk = get_work<kCausal>(P, w);
+          for (int it = 0; ok && it < wk.n_max; ++it, ++g) {
+            const int j = wk.n_max - 1 - it, s = g % kStages;
+            if (!(ok = wait_bar(bars + Bars::k_full + 8 * s, (g / kStages) & 1, abort_s, P.status, 40))) break;
 #pragma unroll
-          for (int t = 0; t < 2; ++t) {
-            if (j < n_t[t]) {
-              const uint16_t* raw = reinterpret_cast<const uint16_t*>(smem + L::dsraw + (s * 2 + t) * 256);
-              uint8_t* dst = smem + L::b1 + (s * 2 + t) * 2048 + (lane >> 3) * 128 + (lane & 7) * 16;   // keys lane + 32 i
+            for (int t = 0; t < 2; ++t) {
+              if (j < wk.n_t[t]) {
+                const uint16_t* raw = reinterpret_cast<const uint16_t*>(smem + L::dsraw + (s * 2 + t) * 256);
+                uint8_t* dst = smem + L::b1 + (s * 2 + t) * 2048 + (lane >> 3) * 128 + (lane & 7) * 16;   // keys lane + 32 i
 #pragma unroll
-              for (int i = 0; i < 4; ++i) *reinterpret_cast<uint16_t*>(dst + i * 512) = raw[lane + 32 * i];
+                for (int i = 0; i < 4; ++i) *reinterpret_cast<uint16_t*>(dst + i * 512) = raw[lane + 32 * i];
+              }
             }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bars + Bars::ds_ready + 8 * s);
           }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bars + Bars::ds_ready + 8 * s);
         }
       } else if (warp == 9 && lane == 0) {
         // ---------------------------------------------------------------- QK issuer
-        // This one thread paces the whole CTA, so its instruction stream is kept minimal: every
-        // shared-memory descriptor is a constant high word (stride / swizzle / version bits) plus a
-        // low word (address >> 4, leading-offset field) that only needs an integer add per use.
+        // This one thread paces the CTA, so its instruction stream is kept minimal: every shared-memory
+        // descriptor is a constant high word (stride / swizzle / version bits) plus a low word
+        // (address >> 4, leading-offset field) that only needs an integer add per use.
         constexpr uint32_t idesc_qk = make_idesc_nvf4(kBlockM, kBlockN);
         constexpr uint32_t idesc_r1 = make_idesc_bf16(kBlockM, kBlockN);
         constexpr uint32_t HI_QK = (kSboQK >> 4) | (1u << 14) | (kSwzQK << 29);
@@ -419,74 +450,53 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         const uint32_t sfq_lo = (sbase + L::sfq) >> 4, sfk_lo = (sbase + L::sfk) >> 4;
         const uint32_t a1_lo = ((sbase + L::a1) >> 4) | (((uint32_t)(L::zero - L::a1) >> 4) << 16);
         const uint32_t b1_lo = ((sbase + L::b1) >> 4) | (((uint32_t)(L::zero - L::b1) >> 4) << 16);
-        const int n0t = n_t[0], n1t = n_t[1];
         bool ok = true;
-        uint32_t pv_cnt[2] = {0, 0}, q_done = 0;
-
-        // S_t = delta_s + Q_t K^T against K stage s (stage resident, tensor-memory proxy fenced)
-        auto issue_qk = [&](const int t, const int s, const bool first_of_it) -> bool {
-          if (!(q_done & (1u << t))) {
-            if (!wait_bar(bars + Bars::q_full + 8 * t, 0, abort_s, P.status, 20)) return false;
-            q_done |= 1u << t;
-            tc_fence_after();
+        uint32_t g = 0;                       // K stages consumed so far
+        uint32_t sq[2] = {0, 0};              // QK groups issued so far per tile slot (= S_t tiles produced)
+        uint32_t qn[2] = {0, 0};              // Q tiles taken so far per slot
+        for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+          const Work wk = get_work<kCausal>(P, w);
+          for (int it = 0; ok && it < wk.n_max; ++it, ++g) {
+            const int j = wk.n_max - 1 - it, s = g % kStages;
+            const uint32_t ph = (g / kStages) & 1;
+            if (!(ok = wait_bar(bars + Bars::k_full + 8 * s, ph, abort_s, P.status, 21))) break;
+            if (has_ds && !(ok = wait_bar(bars + Bars::ds_ready + 8 * s, ph, abort_s, P.status, 25))) break;
+            bool first = true;
 #pragma unroll
-            for (int kb = 0; kb < kKB; ++kb) tc_cp_sf(tm_sfq + 8 * t + 4 * kb, sfq_lo + t * 64 + kb * 32, HI_SF);
-          }
-          if (first_of_it) {
+            for (int t = 0; t < 2; ++t) {
+              if (!ok || j >= wk.n_t[t]) continue;
+              // S_t must be free: the softmax of the previous tile in this slot (this or the previous work
+              // item) has consumed it and signalled p_full
+              if (sq[t] > 0 && !(ok = wait_bar(bars + Bars::p_full + 8 * t, (sq[t] - 1) & 1, abort_s, P.status, 23))) break;
+              if (it == wk.n_max - wk.n_t[t]) {                    // first key tile of this query tile
+                if (!(ok = wait_bar(bars + Bars::q_full + 8 * t, qn[t] & 1, abort_s, P.status, 20))) break;
+                ++qn[t];
+                tc_fence_after();
 #pragma unroll
-            for (int kb = 0; kb < kKB; ++kb) tc_cp_sf(tm_sfk + 4 * kb, sfk_lo + s * 64 + kb * 32, HI_SF);
-          }
-          const uint32_t tm_S = tmem + 128 * t;
-          if (has_ds) {
-            // buffer i sits i*2048 bytes higher, so its distance to the shared zero chunk is i*2048 smaller
-            const uint32_t i = (uint32_t)(s * 2 + t);
-            tc_mma_bf16(tm_S, a1_lo, HI_SF, b1_lo + i * 128u - ((i * 128u) << 16), HI_SF, idesc_r1, 0);
-          }
+                for (int kb = 0; kb < kKB; ++kb) tc_cp_sf(tm_sfq + 8 * t + 4 * kb, sfq_lo + t * 64 + kb * 32, HI_SF);
+              }
+              tc_fence_after();
+              if (first) {
+                first = false;
 #pragma unroll
-          for (int kb = 0; kb < kKB; ++kb)
-            tc_mma_nvf4(tm_S, q_lo + t * (L::kQBytes >> 4) + kb * 2, HI_QK, k_lo + s * (L::kKBytes >> 4) + kb * 2, HI_QK,
-                        idesc_qk, tm_sfq + 8 * t + 4 * kb, tm_sfk + 4 * kb, (has_ds || kb > 0) ? 1u : 0u);
-          tc_commit(bars + Bars::s_full + 8 * t);
-          return true;
-        };
-        auto wait_k = [&](const int it) -> bool {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
-          if (!wait_bar(bars + Bars::k_full + 8 * s, ph, abort_s, P.status, 21)) return false;
-          if (has_ds && !wait_bar(bars + Bars::ds_ready + 8 * s, ph, abort_s, P.status, 25)) return false;
-          tc_fence_after();
-          return true;
-        };
-        // prologue: scores of the first key tile
-        ok = wait_k(0);
-        {
-          const bool a0 = (n_max - 1) < n0t, a1 = (n_max - 1) < n1t;
-          if (ok && a0) ok = issue_qk(0, 0, true);
-          if (ok && a1) ok = issue_qk(1, 0, !a0);
-          if (ok) tc_commit(bars + Bars::k_empty);
-        }
-        int s_next = 1 % kStages;
-        for (int it = 0; ok && it < n_max; ++it) {
-          const int j = n_max - 1 - it;
-          const bool more = it + 1 < n_max;
-          const bool act1n = (j - 1) < n1t;
-          bool k_next_ready = false;
+                for (int kb = 0; kb < kKB; ++kb) tc_cp_sf(tm_sfk + 4 * kb, sfk_lo + s * 64 + kb * 32, HI_SF);
+              }
+              const uint32_t tm_S = tmem + 128 * t;
+              if (has_ds) {
+                // buffer i sits i*2048 bytes higher, so its distance to the shared zero chunk is i*2048 smaller
+                const uint32_t i = (uint32_t)(s * 2 + t);
+                tc_mma_bf16(tm_S, a1_lo, HI_SF, b1_lo + i * 128u - ((i * 128u) << 16), HI_SF, idesc_r1, 0);
+              }
 #pragma unroll
-          for (int t = 0; t < 2; ++t) {
-            const bool act = t == 0 ? (j < n0t) : (j < n1t), actn = t == 0 ? ((j - 1) < n0t) : act1n;
-            // the warpgroup of tile t has consumed S_t (nothing to wait for on the tile's first iteration)
-            if (ok && act) {
-              ok = wait_bar(bars + Bars::p_full + 8 * t, pv_cnt[t] & 1, abort_s, P.status, 23);
-              ++pv_cnt[t];
+              for (int kb = 0; kb < kKB; ++kb)
+                tc_mma_nvf4(tm_S, q_lo + t * (L::kQBytes >> 4) + kb * 2, HI_QK, k_lo + s * (L::kKBytes >> 4) + kb * 2, HI_QK,
+                            idesc_qk, tm_sfq + 8 * t + 4 * kb, tm_sfk + 4 * kb, (has_ds || kb > 0) ? 1u : 0u);
+              tc_commit(bars + Bars::s_full + 8 * t);
+              ++sq[t];
+              if (it == wk.n_max - 1) tc_commit(bars + Bars::q_empty + 8 * t);   // last read of this Q tile
             }
-            if (ok && more && actn) {
-              if (!k_next_ready) ok = wait_k(it + 1);
-              if (ok) ok = issue_qk(t, s_next, !k_next_ready);
-              k_next_ready = true;
-              if (ok && (t == 1 || !act1n)) tc_commit(bars + Bars::k_empty + 8 * s_next);
-            }
+            if (ok) tc_commit(bars + Bars::k_empty + 8 * s);
           }
-          s_next = (s_next + 1 == kStages) ? 0 : s_next + 1;
         }
         if (!ok) {
           // giving up: let every MMA / scale copy already issued finish before tensor memory is freed
@@ -503,38 +513,37 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         constexpr uint32_t LBO1 = 1u << 16;
         const uint32_t p_lo = ((sbase + L::p) >> 4) | LBO1, v_lo = ((sbase + L::v) >> 4) | LBO1;
         const uint32_t sfv_lo = (sbase + L::sfv) >> 4, sfp_lo = (sbase + L::sfp) >> 4;
-        const int n0t = n_t[0], n1t = n_t[1];
         bool ok = true;
-        uint32_t pv_cnt[2] = {0, 0}, pv_total = 0, ph = 0;
-        int s = 0;
-        for (int it = 0; ok && it < n_max; ++it) {
-          const int j = n_max - 1 - it;
-          const bool act1 = j < n1t;
-          // the V stage and its scale factors do not depend on the softmax: fetch them before waiting for P
-          if (!(ok = wait_bar(bars + Bars::v_full + 8 * s, ph, abort_s, P.status, 24))) break;
-          tc_fence_after();
-#pragma unroll
-          for (int kb = 0; kb < 2; ++kb) tc_cp_sf(tm_sfv + 4 * kb, sfv_lo + s * 64 + kb * 32, HI_SF);
-#pragma unroll
-          for (int t = 0; t < 2; ++t) {
-            const bool act = t == 0 ? (j < n0t) : act1;
-            if (!(ok && act)) continue;
-            if (!(ok = wait_bar(bars + Bars::p_full + 8 * t, pv_cnt[t] & 1, abort_s, P.status, 26))) break;
-            if (pv_total > 0 && !(ok = wait_bar(bars + Bars::o_free, (pv_total - 1) & 1, abort_s, P.status, 22))) break;
+        uint32_t g = 0, pv_cnt[2] = {0, 0}, pv_total = 0;
+        for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+          const Work wk = get_work<kCausal>(P, w);
+          for (int it = 0; ok && it < wk.n_max; ++it, ++g) {
+            const int j = wk.n_max - 1 - it, s = g % kStages;
+            const bool act1 = j < wk.n_t[1];
+            // the V stage and its scale factors do not depend on the softmax: fetch them before waiting for P
+            if (!(ok = wait_bar(bars + Bars::v_full + 8 * s, (g / kStages) & 1, abort_s, P.status, 24))) break;
             tc_fence_after();
 #pragma unroll
-            for (int kb = 0; kb < 2; ++kb) tc_cp_sf(tm_sfp + 8 * t + 4 * kb, sfp_lo + t * 64 + kb * 32, HI_SF);
+            for (int kb = 0; kb < 2; ++kb) tc_cp_sf(tm_sfv + 4 * kb, sfv_lo + s * 64 + kb * 32, HI_SF);
 #pragma unroll
-            for (int kb = 0; kb < 2; ++kb)
-              tc_mma_nvf4(tm_O, p_lo + t * (L::kPBytes >> 4) + kb * 2, HI_PV, v_lo + s * (L::kVBytes >> 4) + kb * 2, HI_PV,
-                          idesc_pv, tm_sfp + 8 * t + 4 * kb, tm_sfv + 4 * kb, kb > 0);
-            tc_commit(bars + Bars::o_full + 8 * t);
-            ++pv_cnt[t];
-            ++pv_total;
-            if (t == 1 || !act1) tc_commit(bars + Bars::v_empty + 8 * s);   // last PV of this stage
+            for (int t = 0; t < 2; ++t) {
+              const bool act = t == 0 ? (j < wk.n_t[0]) : act1;
+              if (!(ok && act)) continue;
+              if (!(ok = wait_bar(bars + Bars::p_full + 8 * t, pv_cnt[t] & 1, abort_s, P.status, 26))) break;
+              if (pv_total > 0 && !(ok = wait_bar(bars + Bars::o_free, (pv_total - 1) & 1, abort_s, P.status, 22))) break;
+              tc_fence_after();
+#pragma unroll
+              for (int kb = 0; kb < 2; ++kb) tc_cp_sf(tm_sfp + 8 * t + 4 * kb, sfp_lo + t * 64 + kb * 32, HI_SF);
+#pragma unroll
+              for (int kb = 0; kb < 2; ++kb)
+                tc_mma_nvf4(tm_O, p_lo + t * (L::kPBytes >> 4) + kb * 2, HI_PV, v_lo + s * (L::kVBytes >> 4) + kb * 2, HI_PV,
+                            idesc_pv, tm_sfp + 8 * t + 4 * kb, tm_sfv + 4 * kb, kb > 0);
+              tc_commit(bars + Bars::o_full + 8 * t);
+              ++pv_cnt[t];
+              ++pv_total;
+              if (t == 1 || !act1) tc_commit(bars + Bars::v_empty + 8 * s);   // last PV of this stage
+            }
           }
-          s = (s + 1 == kStages) ? 0 : s + 1;
-          if (s == 0) ph ^= 1;
         }
         if (!ok) {
           tc_commit(bars + Bars::drain + 8);
@@ -542,35 +551,67 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         }
       }
     } else {
-      // ------------------------------------------------------------------ exp / quantise + O accumulation
+      // ------------------------------------------------------------------ softmax + O accumulation
       asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
-      const int t = warp >> 2;                                   // query tile of this warpgroup
+      const int t = warp >> 2;                                   // query tile slot of this warpgroup
       const int row = threadIdx.x & 127;                         // tensor-memory lane
-      const int n_mine = n_t[t];
-      const int qt = 2 * pair + t;
-      const int q0 = qt * kBlockM, qpos = q0 + row;
-      if (n_mine > 0) {
-        const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-        const uint32_t tm_S = tmem + 128 * t + lane_addr;
+      const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+      const uint32_t tm_S = tmem + 128 * t + lane_addr;
+      const float c = P.scale_log2;
+      uint8_t* p_row = smem + L::p + t * L::kPBytes + row * 64;
+      const int swz = (row >> 1) & 3;
+      float2* st = reinterpret_cast<float2*>(smem + L::stats) + t * 8 * 128 + row;
+      uint32_t* sfp_row = reinterpret_cast<uint32_t*>(smem + L::sfp + t * 1024 + sf_atom_offset(row, 0));
+      const uint32_t bar_s = bars + Bars::s_full + 8 * t, bar_p = bars + Bars::p_full + 8 * t;
+      const uint32_t bar_o = bars + Bars::o_full + 8 * t;
+      uint32_t sc = 0;                                           // key tiles processed so far by this warpgroup
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+        const Work wk = get_work<kCausal>(P, w);
+        const int n_mine = wk.n_t[t];
+        const int qt = 2 * wk.pair + t;
+        const int q0 = qt * kBlockM, qpos = q0 + row;
+        __nv_bfloat16* orow = P.out + wk.b * P.o_sb + wk.hq * P.o_sh + (int64_t)qpos * P.o_sn;
+        if (n_mine == 0) {
+          // query tile that sees no key at all (causal, more queries than keys): zeros, like the
+          // reference's store_zero (fwd_epilogue.cu:150-183); nothing if the tile does not exist
+          if (qt < P.Tq && qpos < P.Nq) {
+            for (int i = 0; i < D / 8; ++i) reinterpret_cast<uint4*>(orow)[i] = make_uint4(0, 0, 0, 0);
+            if (P.lse) P.lse[((int64_t)wk.b * P.Hq + wk.hq) * P.Nq + qpos] = INFINITY;
+          }
+          continue;
+        }
         const int key_lim = min(P.Nk - 1, kCausal ? qpos + P.Nk - P.Nq : 0x7fffffff);   // last visible key
-        const float c = P.scale_log2;
         float2 O2[D / 2];
 #pragma unroll
         for (int i = 0; i < D / 2; ++i) O2[i] = make_float2(0.f, 0.f);
         float m = -INFINITY, l = 0.f;                            // m in raw score units
-        uint8_t* p_row = smem + L::p + t * L::kPBytes + row * 64;
-        const int swz = (row >> 1) & 3;
-        float2* st = reinterpret_cast<float2*>(smem + L::stats) + t * 8 * 128 + row;
-        uint32_t* sfp_row = reinterpret_cast<uint32_t*>(smem + L::sfp + t * 1024 + sf_atom_offset(row, 0));
-        const uint32_t bar_s = bars + Bars::s_full + 8 * t, bar_p = bars + Bars::p_full + 8 * t;
-        const uint32_t bar_o = bars + Bars::o_full + 8 * t;
-        bool ok = true;
 
-        // O = O * alpha + (P^ V^ of one key tile), product read from tensor memory 16 columns at a time
-        // with the next load in flight; the shared product buffer is released as soon as it is in registers
-        auto fold_product = [&](const float alpha_) {
+        for (int it = 0; it < n_mine; ++it, ++sc) {
+          const int j = n_mine - 1 - it;
+          const int n0 = j * kBlockN;
+          const bool need_mask = (n0 + kBlockN - 1 >= P.Nk) || (kCausal && n0 + kBlockN - 1 > q0 + P.Nk - P.Nq);
+          if (!(ok = wait_bar(bar_s, sc & 1, abort_s, P.status, 30))) break;
           tc_fence_after();
-          const float2 al2 = make_float2(alpha_, alpha_);
+          uint2 sfp;
+          const float alpha = need_mask ? softmax_pass1_masked(tm_S, c, m, st, sfp, n0, key_lim)
+                                        : softmax_pass1_impl<false>(tm_S, c, m, st, sfp, 0, 0);
+          sfp_row[0] = sfp.x;
+          sfp_row[128] = sfp.y;
+          if (need_mask) softmax_pass2_masked(tm_S, c, alpha, l, st, p_row, swz, n0, key_lim);
+          else softmax_pass2_impl<false>(tm_S, c, alpha, l, st, p_row, swz, 0, 0);
+          // S consumed and P^ written: hand both to the MMA issuers
+          tc_fence_before();
+          fence_proxy_async_smem();
+          mbar_arrive(bar_p);
+          // While the QK MMA of the next key tile is issued and runs, the P.V product of this one
+          // (issued by the other issuer thread at the same time) is folded into O.  Its completion
+          // also means P^ and its scales may be overwritten by the next iteration.
+          if (!(ok = wait_bar(bar_o, sc & 1, abort_s, P.status, 31))) break;
+          // O = O * alpha + (P^ V^ of this key tile), read from tensor memory 16 columns at a time with the
+          // next load in flight; the shared product buffer is released as soon as it is in registers
+          tc_fence_after();
+          const float2 al2 = make_float2(alpha, alpha);
           uint32_t ra[16], rb[16];
           tmem_ld16(tm_O + lane_addr, ra);
 #pragma unroll
@@ -591,36 +632,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
             for (int i = 0; i < 8; ++i)
               O2[(ch + 1) * 8 + i] = ffma2(O2[(ch + 1) * 8 + i], al2, make_float2(__uint_as_float(rb[2 * i]), __uint_as_float(rb[2 * i + 1])));
           }
-        };
-
-        for (int it = 0; it < n_mine; ++it) {
-          const int j = n_mine - 1 - it;
-          const int n0 = j * kBlockN;
-          const bool need_mask = (n0 + kBlockN - 1 >= P.Nk) || (kCausal && n0 + kBlockN - 1 > q0 + P.Nk - P.Nq);
-          if (!(ok = wait_bar(bar_s, it & 1, abort_s, P.status, 30))) break;
-          tc_fence_after();
-          uint2 sfp;
-          const float alpha = need_mask ? softmax_pass1_masked(tm_S, c, m, st, sfp, n0, key_lim)
-                                        : softmax_pass1_impl<false>(tm_S, c, m, st, sfp, 0, 0);
-          sfp_row[0] = sfp.x;
-          sfp_row[128] = sfp.y;
-          if (need_mask) softmax_pass2_masked(tm_S, c, alpha, l, st, p_row, swz, n0, key_lim);
-          else softmax_pass2_impl<false>(tm_S, c, alpha, l, st, p_row, swz, 0, 0);
-          // S consumed and P^ written: hand both to the MMA issuers
-          tc_fence_before();
-          fence_proxy_async_smem();
-          mbar_arrive(bar_p);
-          // While the QK MMA of the next key tile is issued and runs, the P.V product of this one
-          // (issued by the other issuer thread at the same time) is folded into O.  Its completion
-          // also means P^ and its scales may be overwritten by the next iteration.
-          if (!(ok = wait_bar(bar_o, it & 1, abort_s, P.status, 31))) break;
-          fold_product(alpha);
         }
 
         // ---- epilogue: O / l -> bf16 -> global (row-contiguous 16-byte stores)
         if (ok && qpos < P.Nq) {
           const float inv = (l == 0.f || l != l) ? 0.f : 1.0f / l;
-          __nv_bfloat16* orow = P.out + b * P.o_sb + hq * P.o_sh + (int64_t)qpos * P.o_sn;
 #pragma unroll
           for (int i = 0; i < D / 8; ++i) {
             uint4 o;
@@ -632,22 +648,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           }
           if (P.lse) {
             // natural-log sum of exp(sm_scale * s) over the row (l carries the factor 2688)
-            P.lse[((int64_t)b * P.Hq + hq) * P.Nq + qpos] =
+            P.lse[((int64_t)wk.b * P.Hq + wk.hq) * P.Nq + qpos] =
                 (l == 0.f) ? -INFINITY : (m * c + log2f(l) + kLog2Inv2688) * (1.0f / kLog2e);
           }
         }
       }
-    }
-  }
-  // query tiles that see no key at all (causal, more queries than keys): zeros, like the
-  // reference's store_zero (fwd_epilogue.cu:150-183)
-  if (run && warp < 8) {
-    const int t = warp >> 2, qt = 2 * pair + t;
-    const int qpos = qt * kBlockM + (threadIdx.x & 127);
-    if (qt < P.Tq && n_t[t] == 0 && qpos < P.Nq) {
-      __nv_bfloat16* orow = P.out + b * P.o_sb + hq * P.o_sh + (int64_t)qpos * P.o_sn;
-      for (int i = 0; i < D / 8; ++i) reinterpret_cast<uint4*>(orow)[i] = make_uint4(0, 0, 0, 0);
-      if (P.lse) P.lse[((int64_t)b * P.Hq + hq) * P.Nq + qpos] = INFINITY;
     }
   }
 
@@ -708,7 +713,12 @@ cudaError_t launch(const AttnArgs& a, cudaStream_t stream) {
   auto kern = attn_fwd_kernel<D, kCausal>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total + 1024);
   if (e != cudaSuccess) return e;
-  const int64_t grid = (int64_t)a.B * a.Hq * ((Tq + 1) / 2);
+  // persistent CTAs: one per SM (registers and tensor memory allow exactly one), each walks the work list
+  int dev = 0, sms = 0;
+  if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+  if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+  const int64_t work = (int64_t)a.B * a.Hq * ((Tq + 1) / 2);
+  const int64_t grid = work < sms ? work : sms;
   kern<<<(unsigned)grid, kAttnThreads, L::total + 1024, stream>>>(tq, tk, tv, P);
   return cudaGetLastError();
 }
