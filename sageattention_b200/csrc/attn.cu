@@ -255,13 +255,30 @@ struct Work {
   int n_max;
 };
 
+// Static schedule: in round r CTA i takes item r*G + i, odd rounds in reverse CTA order, so a CTA that got
+// the heaviest item of one round gets the lightest of the next.  Returns -1 when the CTA is done.
+__device__ __forceinline__ int work_at(const int r, const int total) {
+  const int G = (int)gridDim.x, i = (int)blockIdx.x;
+  const int w = r * G + ((r & 1) ? G - 1 - i : i);
+  return w < total ? w : -1;
+}
+
 template <bool kCausal>
 __device__ __forceinline__ Work get_work(const KParams& P, const int w) {
   Work k;
   const int n_pairs = (P.Tq + 1) >> 1;
-  // pairs of one head are adjacent in the work list (they share K/V in L2); the longest causal pairs first
-  k.pair = n_pairs - 1 - (w % n_pairs);
-  const int bh = w / n_pairs;
+  int bh;
+  if (kCausal) {
+    // item cost grows with the pair index: heaviest pairs of all heads first, so that the rounds of
+    // the static schedule hand out work of falling, nearly equal cost
+    const int n_bh = P.B * P.Hq;
+    k.pair = n_pairs - 1 - w / n_bh;
+    bh = w % n_bh;
+  } else {
+    // equal cost: keep the pairs of one head adjacent in time (they share K/V in L2)
+    k.pair = n_pairs - 1 - (w % n_pairs);
+    bh = w / n_pairs;
+  }
   k.b = bh / P.Hq;
   k.hq = bh % P.Hq;
   k.hkv = k.hq / (P.Hq / P.Hkv);
@@ -360,7 +377,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         uint32_t gk = 0;                      // K stages issued so far (g or g + 1)
         uint32_t qn[2] = {0, 0};              // Q tiles loaded so far per slot
         bool ok = true;
-        for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+        for (int r = 0, w; ok && (w = work_at(r, total_work)) >= 0; ++r) {
           const Work wk = get_work<kCausal>(P, w);
           int64_t ds_row[2];
 #pragma unroll
@@ -417,7 +434,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         // element sits at (n/8)*128 + (n%8)*16; everything else stays zero.
         uint32_t g = 0;
         bool ok = true;
-        for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+        for (int r = 0, w; ok && (w = work_at(r, total_work)) >= 0; ++r) {
           const Work wk = get_work<kCausal>(P, w);
           for (int it = 0; ok && it < wk.n_max; ++it, ++g) {
             const int j = wk.n_max - 1 - it, s = g % kStages;
@@ -454,7 +471,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         uint32_t g = 0;                       // K stages consumed so far
         uint32_t sq[2] = {0, 0};              // QK groups issued so far per tile slot (= S_t tiles produced)
         uint32_t qn[2] = {0, 0};              // Q tiles taken so far per slot
-        for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+        for (int r = 0, w; ok && (w = work_at(r, total_work)) >= 0; ++r) {
           const Work wk = get_work<kCausal>(P, w);
           for (int it = 0; ok && it < wk.n_max; ++it, ++g) {
             const int j = wk.n_max - 1 - it, s = g % kStages;
@@ -515,7 +532,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         const uint32_t sfv_lo = (sbase + L::sfv) >> 4, sfp_lo = (sbase + L::sfp) >> 4;
         bool ok = true;
         uint32_t g = 0, pv_cnt[2] = {0, 0}, pv_total = 0;
-        for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+        for (int r = 0, w; ok && (w = work_at(r, total_work)) >= 0; ++r) {
           const Work wk = get_work<kCausal>(P, w);
           for (int it = 0; ok && it < wk.n_max; ++it, ++g) {
             const int j = wk.n_max - 1 - it, s = g % kStages;
@@ -566,7 +583,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       const uint32_t bar_o = bars + Bars::o_full + 8 * t;
       uint32_t sc = 0;                                           // key tiles processed so far by this warpgroup
       bool ok = true;
-      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+      for (int r = 0, w; ok && (w = work_at(r, total_work)) >= 0; ++r) {
         const Work wk = get_work<kCausal>(P, w);
         const int n_mine = wk.n_t[t];
         const int qt = 2 * wk.pair + t;
