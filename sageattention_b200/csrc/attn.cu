@@ -49,6 +49,11 @@ constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
 constexpr int kStages = 3;
 constexpr int kAttnThreads = 384;
+// Register hand-over (setmaxnreg) moves registers inside the pool the CTA was LAUNCHED with; a request beyond
+// it would block forever, so the split is checked here.  kLaunchRegs is what the compiler allocates under
+// __launch_bounds__(384, 1).
+constexpr int kLaunchRegs = 168, kSoftmaxRegs = 224, kRoleRegs = 56;
+static_assert(256 * kSoftmaxRegs + 128 * kRoleRegs <= kAttnThreads * kLaunchRegs, "setmaxnreg split exceeds the CTA's register pool");
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLog2Inv2688 = -11.392317422778762f;   // log2(1 / (448 * 6))  softmax_fused.h:33
 constexpr float kLog2Inv6 = -2.584962500721156f;       // log2(1 / 6)          softmax_fused.h:34
@@ -108,10 +113,13 @@ struct KParams {
   float scale_log2;      // sm_scale * log2(e)
 };
 
-// wait with a poll limit; also gives up as soon as any CTA has reported a failure
+// Bounded wait on an mbarrier phase; also gives up as soon as any CTA has reported a failure.  A failing poll
+// parks the thread for about 1.5 us (kHinted: about 4 us), so the limit is 3 to 8 seconds; which flavour is
+// faster was measured per role: the shorter park costs issue slots but reacts sooner.
+template <bool kHinted>
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_s, int* status, int code) {
-  for (uint32_t i = 0; i < (1u << 22); ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+  for (uint32_t i = 0; i < (1u << 21); ++i) {
+    if (mbar_try_wait<kHinted ? 20000 : 0>(bar, parity)) return true;
     if ((i & 1023u) == 1023u && (*abort_s != 0 || *reinterpret_cast<volatile int*>(status) != 0)) break;
   }
   *abort_s = 1;
@@ -309,6 +317,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
   constexpr int kKB = D / 64;                              // K=64 blocks of the QK contraction
   constexpr uint32_t kSwzQK = (D == 128) ? 4u : 6u;        // 64-byte / 32-byte swizzle
   constexpr uint32_t kSboQK = (D == 128) ? 512u : 256u;
+  constexpr bool kIssuerHint = (D == 64);                  // the MMA issuers of the D=64 kernel do better with the longer park
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // swizzled tiles need 1024-byte alignment
   const uint32_t sbase = smem_u32(smem);
@@ -369,7 +378,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
   // next item start while the tail of the current one is still being finished.
   if (run) {
     if (warp >= 8) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRoleRegs));
       if (warp == 8 && lane == 0) {
         // ---------------------------------------------------------------- TMA producer
         prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
@@ -386,7 +395,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
             ds_row[t] = ((int64_t)wk.b * P.Hq + wk.hq) * P.ds_rows + (P.ds_rows == 1 ? 0 : qt);
             if (ok && wk.n_t[t] > 0) {
               // the slot's previous Q tile must have been read by its last QK MMA
-              if (qn[t] > 0 && !(ok = wait_bar(bars + Bars::q_empty + 8 * t, (qn[t] - 1) & 1, abort_s, P.status, 12))) break;
+              if (qn[t] > 0 && !(ok = wait_bar<false>(bars + Bars::q_empty + 8 * t, (qn[t] - 1) & 1, abort_s, P.status, 12))) break;
               const int64_t qtile = ((int64_t)wk.b * P.Hq + wk.hq) * P.Tq + qt;
               const uint32_t qb = bars + Bars::q_full + 8 * t;
               mbar_arrive_expect_tx(qb, L::kQBytes + L::kSfRow);
@@ -399,7 +408,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           for (int it = 0; ok && it < wk.n_max; ++it, ++g) {
             const int j = wk.n_max - 1 - it, s = g % kStages;
             const uint32_t ph = ((g / kStages) & 1) ^ 1;
-            if (!(ok = wait_bar(bars + Bars::k_empty + 8 * s, ph, abort_s, P.status, 10))) break;
+            if (!(ok = wait_bar<false>(bars + Bars::k_empty + 8 * s, ph, abort_s, P.status, 10))) break;
             const uint32_t kb = bars + Bars::k_full + 8 * s;
             const int nds = has_ds ? (int)(j < wk.n_t[0]) + (int)(j < wk.n_t[1]) : 0;
             mbar_arrive_expect_tx(kb, L::kKBytes + L::kSfRow + 256 * nds);
@@ -412,7 +421,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
                   bulk_load(sbase + L::dsraw + (s * 2 + t) * 256, P.ds + (ds_row[t] * P.Tk + j) * kBlockN, 256, kb);
             }
             ++gk;
-            if (!(ok = wait_bar(bars + Bars::v_empty + 8 * s, ph, abort_s, P.status, 11))) break;
+            if (!(ok = wait_bar<false>(bars + Bars::v_empty + 8 * s, ph, abort_s, P.status, 11))) break;
             const uint32_t vb = bars + Bars::v_full + 8 * s;
             mbar_arrive_expect_tx(vb, L::kVBytes + L::kSfV);
             tma_load_2d(sbase + L::v + s * L::kVBytes, &tm_v, 0, (int)((kvhead + j) * D), vb);
@@ -422,11 +431,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         if (*abort_s) {
           // giving up: the copies this thread started must land before the CTA may exit
           for (int t = 0; t < 2; ++t)
-            if (qn[t] > 0) mbar_wait(bars + Bars::q_full + 8 * t, (qn[t] - 1) & 1, 1u << 20);
+            if (qn[t] > 0) mbar_wait(bars + Bars::q_full + 8 * t, (qn[t] - 1) & 1, 1u << 16);
           for (uint32_t i = (gk > (uint32_t)kStages ? gk - kStages : 0); i < gk; ++i)
-            mbar_wait(bars + Bars::k_full + 8 * (i % kStages), (i / kStages) & 1, 1u << 20);
+            mbar_wait(bars + Bars::k_full + 8 * (i % kStages), (i / kStages) & 1, 1u << 16);
           for (uint32_t i = (g > (uint32_t)kStages ? g - kStages : 0); i < g; ++i)
-            mbar_wait(bars + Bars::v_full + 8 * (i % kStages), (i / kStages) & 1, 1u << 20);
+            mbar_wait(bars + Bars::v_full + 8 * (i % kStages), (i / kStages) & 1, 1u << 16);
         }
       } else if (warp == 10 && has_ds) {
         // ---------------------------------------------------------------- delta_s -> rank-1 B operand
@@ -438,7 +447,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           const Work wk = get_work<kCausal>(P, w);
           for (int it = 0; ok && it < wk.n_max; ++it, ++g) {
             const int j = wk.n_max - 1 - it, s = g % kStages;
-            if (!(ok = wait_bar(bars + Bars::k_full + 8 * s, (g / kStages) & 1, abort_s, P.status, 40))) break;
+            if (!(ok = wait_bar<false>(bars + Bars::k_full + 8 * s, (g / kStages) & 1, abort_s, P.status, 40))) break;
 #pragma unroll
             for (int t = 0; t < 2; ++t) {
               if (j < wk.n_t[t]) {
@@ -476,17 +485,17 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           for (int it = 0; ok && it < wk.n_max; ++it, ++g) {
             const int j = wk.n_max - 1 - it, s = g % kStages;
             const uint32_t ph = (g / kStages) & 1;
-            if (!(ok = wait_bar(bars + Bars::k_full + 8 * s, ph, abort_s, P.status, 21))) break;
-            if (has_ds && !(ok = wait_bar(bars + Bars::ds_ready + 8 * s, ph, abort_s, P.status, 25))) break;
+            if (!(ok = wait_bar<kIssuerHint>(bars + Bars::k_full + 8 * s, ph, abort_s, P.status, 21))) break;
+            if (has_ds && !(ok = wait_bar<kIssuerHint>(bars + Bars::ds_ready + 8 * s, ph, abort_s, P.status, 25))) break;
             bool first = true;
 #pragma unroll
             for (int t = 0; t < 2; ++t) {
               if (!ok || j >= wk.n_t[t]) continue;
               // S_t must be free: the softmax of the previous tile in this slot (this or the previous work
               // item) has consumed it and signalled p_full
-              if (sq[t] > 0 && !(ok = wait_bar(bars + Bars::p_full + 8 * t, (sq[t] - 1) & 1, abort_s, P.status, 23))) break;
+              if (sq[t] > 0 && !(ok = wait_bar<kIssuerHint>(bars + Bars::p_full + 8 * t, (sq[t] - 1) & 1, abort_s, P.status, 23))) break;
               if (it == wk.n_max - wk.n_t[t]) {                    // first key tile of this query tile
-                if (!(ok = wait_bar(bars + Bars::q_full + 8 * t, qn[t] & 1, abort_s, P.status, 20))) break;
+                if (!(ok = wait_bar<kIssuerHint>(bars + Bars::q_full + 8 * t, qn[t] & 1, abort_s, P.status, 20))) break;
                 ++qn[t];
                 tc_fence_after();
 #pragma unroll
@@ -518,7 +527,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         if (!ok) {
           // giving up: let every MMA / scale copy already issued finish before tensor memory is freed
           tc_commit(bars + Bars::drain);
-          mbar_wait(bars + Bars::drain, 0, 1u << 20);
+          mbar_wait(bars + Bars::drain, 0, 1u << 16);
         }
       } else if (warp == 11 && lane == 0) {
         // ---------------------------------------------------------------- PV issuer
@@ -538,7 +547,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
             const int j = wk.n_max - 1 - it, s = g % kStages;
             const bool act1 = j < wk.n_t[1];
             // the V stage and its scale factors do not depend on the softmax: fetch them before waiting for P
-            if (!(ok = wait_bar(bars + Bars::v_full + 8 * s, (g / kStages) & 1, abort_s, P.status, 24))) break;
+            if (!(ok = wait_bar<kIssuerHint>(bars + Bars::v_full + 8 * s, (g / kStages) & 1, abort_s, P.status, 24))) break;
             tc_fence_after();
 #pragma unroll
             for (int kb = 0; kb < 2; ++kb) tc_cp_sf(tm_sfv + 4 * kb, sfv_lo + s * 64 + kb * 32, HI_SF);
@@ -546,8 +555,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
             for (int t = 0; t < 2; ++t) {
               const bool act = t == 0 ? (j < wk.n_t[0]) : act1;
               if (!(ok && act)) continue;
-              if (!(ok = wait_bar(bars + Bars::p_full + 8 * t, pv_cnt[t] & 1, abort_s, P.status, 26))) break;
-              if (pv_total > 0 && !(ok = wait_bar(bars + Bars::o_free, (pv_total - 1) & 1, abort_s, P.status, 22))) break;
+              if (!(ok = wait_bar<kIssuerHint>(bars + Bars::p_full + 8 * t, pv_cnt[t] & 1, abort_s, P.status, 26))) break;
+              if (pv_total > 0 && !(ok = wait_bar<kIssuerHint>(bars + Bars::o_free, (pv_total - 1) & 1, abort_s, P.status, 22))) break;
               tc_fence_after();
 #pragma unroll
               for (int kb = 0; kb < 2; ++kb) tc_cp_sf(tm_sfp + 8 * t + 4 * kb, sfp_lo + t * 64 + kb * 32, HI_SF);
@@ -564,12 +573,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         }
         if (!ok) {
           tc_commit(bars + Bars::drain + 8);
-          mbar_wait(bars + Bars::drain + 8, 0, 1u << 20);
+          mbar_wait(bars + Bars::drain + 8, 0, 1u << 16);
         }
       }
     } else {
       // ------------------------------------------------------------------ softmax + O accumulation
-      asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
       const int t = warp >> 2;                                   // query tile slot of this warpgroup
       const int row = threadIdx.x & 127;                         // tensor-memory lane
       const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
@@ -608,7 +617,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           const int j = n_mine - 1 - it;
           const int n0 = j * kBlockN;
           const bool need_mask = (n0 + kBlockN - 1 >= P.Nk) || (kCausal && n0 + kBlockN - 1 > q0 + P.Nk - P.Nq);
-          if (!(ok = wait_bar(bar_s, sc & 1, abort_s, P.status, 30))) break;
+          if (!(ok = wait_bar<false>(bar_s, sc & 1, abort_s, P.status, 30))) break;
           tc_fence_after();
           uint2 sfp;
           const float alpha = need_mask ? softmax_pass1_masked(tm_S, c, m, st, sfp, n0, key_lim)
@@ -624,7 +633,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           // While the QK MMA of the next key tile is issued and runs, the P.V product of this one
           // (issued by the other issuer thread at the same time) is folded into O.  Its completion
           // also means P^ and its scales may be overwritten by the next iteration.
-          if (!(ok = wait_bar(bar_o, sc & 1, abort_s, P.status, 31))) break;
+          if (!(ok = wait_bar<false>(bar_o, sc & 1, abort_s, P.status, 31))) break;
           // O = O * alpha + (P^ V^ of this key tile), read from tensor memory 16 columns at a time with the
           // next load in flight; the shared product buffer is released as soon as it is in registers
           tc_fence_after();

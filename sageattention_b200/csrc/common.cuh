@@ -122,16 +122,31 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// A waiting thread is parked by the hardware for up to this long (it is woken as soon as the phase
-// completes), so waiting warps do not spin through the issue slots of the warps that do the work.
-constexpr uint32_t kSuspendHintNs = 20000;
+// One poll of an mbarrier phase.  kHintNs > 0: try_wait with a suspend-time hint (measured on B200: a failing
+// poll returns after about 4 us whatever the hint); 0: try_wait without hint (about 1.5 us); < 0: a plain test
+// that never parks (7 ns).  A parked thread resumes as soon as the phase completes.
+template <int kHintNs = 0>
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
-      "selp.u32 %0, 1, 0, p;\n}"
-      : "=r"(ok) : "r"(bar), "r"(parity), "r"(kSuspendHintNs) : "memory");
+  if constexpr (kHintNs > 0) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"((uint32_t)kHintNs) : "memory");
+  } else if constexpr (kHintNs == 0) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  } else {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  }
   return ok != 0;
 }
 // Bounded wait: gives up after `limit` polls and reports failure instead of hanging the SM.
