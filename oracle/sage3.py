@@ -11,8 +11,10 @@ by line but cannot be checked against a run of the reference kernel on this hard
 
 Reference paths (inside ``sageattention3_blackwell/``):
 
-* preprocessing ``sageattn4/api.py:179-205`` without the K-packing steps ``quant_pack_k`` /
-  ``quant_pack_v`` (:193-194), which belong to the fork's SageAttention4 extension: K minus its
+* the K-packing steps ``quant_pack_k`` / ``quant_pack_v`` (api.py:122-177, :193-194) of the fork's
+  SageAttention4 extension are restated separately (``pack_k``, ``pack_v``, ``sageattn4_emulated``;
+  the packing is pinned by golden vectors made with the reference's own ``preprocess_qkv``).
+* preprocessing ``sageattn4/api.py:179-205`` without those packing steps: K minus its
   per-channel mean over tokens (:184), Q padded to 128 and minus its per-128-token mean
   (:26-72, :186-191), ``delta_s = qm @ k^T`` in bf16 then widened to fp32 (:201), zero padding
   of K and V to a multiple of 128 (:196-203).
@@ -115,13 +117,18 @@ def _e2m1_round(x: torch.Tensor) -> torch.Tensor:
 
 def attention_quantised(qd: torch.Tensor, kd: torch.Tensor, vtd: torch.Tensor, delta_s: torch.Tensor,
                         len_q: int, len_k: int, sm_scale: float, causal: bool = False,
-                        return_lse: bool = False):
+                        return_lse: bool = False, lamb: torch.Tensor | None = None):
     """Flash-style forward on de-quantised operands with the reference's P re-quantisation.
 
     qd  [B,Hq,Nq_pad,D]  fp32 = dequantised Q codes
     kd  [B,Hk,Nk_pad,D]  fp32 = dequantised K codes
     vtd [B,Hk,D,Nk_pad]  fp32 = dequantised V^T codes
     delta_s [B,Hq,Nq_pad/128,Nk_pad] fp32 (or None)
+    lamb [B,Hk,Nk_pad] fp32 (or None): K-packing mode (fwd_mainloop.cu:796-891).  Keys then come in
+    groups of 16 = one mean slot + 15 residual tokens, ``len_k`` is the PACKED length, every score
+    gets ``lamb * (score of its group's mean slot)`` added before masking, the causal mask works on the
+    logical token of each packed key (:273-281, :921-934) and the mean slot itself is masked out
+    (:878-881, per-block-mean variant).
     Returns O [B,Hq,len_q,D] fp32 (callers round to bf16) and optionally the log-sum-exp
     (natural log, of the smoothed scores) [B,Hq,len_q].
     """
@@ -131,6 +138,9 @@ def attention_quantised(qd: torch.Tensor, kd: torch.Tensor, vtd: torch.Tensor, d
     if g > 1:
         kd = kd.repeat_interleave(g, dim=1)
         vtd = vtd.repeat_interleave(g, dim=1)
+        if lamb is not None:
+            lamb = lamb.repeat_interleave(g, dim=1)
+    len_k_logical = packed_len_to_logical(len_k) if lamb is not None else len_k
     nqb, nkb = Nq // BLOCK, Nk // BLOCK
     c = sm_scale * LOG2E
     q4 = qd.reshape(B, Hq, nqb, BLOCK, D)
@@ -144,9 +154,18 @@ def attention_quantised(qd: torch.Tensor, kd: torch.Tensor, vtd: torch.Tensor, d
         if delta_s is not None:
             S = S + delta_s[:, :, :, None, j * BLOCK:(j + 1) * BLOCK]
         kpos = torch.arange(j * BLOCK, (j + 1) * BLOCK)
+        ktok = kpos
+        if lamb is not None:                               # correct_lamb_k, fwd_mainloop.cu:796-845
+            S16 = S.reshape(B, Hq, nqb, BLOCK, BLOCK // 16, 16)
+            lam16 = lamb[:, :, j * BLOCK:(j + 1) * BLOCK].reshape(B, Hq, 1, 1, BLOCK // 16, 16)
+            S = (S16 + lam16 * S16[..., :1]).reshape(B, Hq, nqb, BLOCK, BLOCK)
+            lane = kpos % 16
+            ktok = (kpos // 16) * 15 + torch.where(lane == 0, lane, lane - 1)   # :273-281
         mask = (kpos >= len_k)[None, None, :].expand(nqb, BLOCK, BLOCK)
         if causal:                                         # fwd_mainloop.cu:926
-            mask = mask | (kpos[None, None, :] >= (qpos[:, :, None] + 1 + len_k - len_q))
+            mask = mask | (ktok[None, None, :] >= (qpos[:, :, None] + 1 + len_k_logical - len_q))
+        if lamb is not None:                               # the mean slot carries no token (:878-881)
+            mask = mask | (kpos % 16 == 0)[None, None, :]
         if causal and bool(mask.all()):
             continue                                       # tile never visited (get_n_block_max :305-324)
         S = S.masked_fill(mask, -math.inf)
@@ -205,6 +224,75 @@ def sageattn3_emulated(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_cau
         lse = lse + sm_scale * torch.matmul(q.float(), km_rep.float().transpose(-2, -1)).squeeze(-1)
         return out.to(q.dtype), lse
     return res.to(q.dtype)
+
+
+# ---------------------------------------------------------------------------------------------
+# K-packing mode of the fork (SageAttention4): api.py:122-177, 193-203, 267-274
+# ---------------------------------------------------------------------------------------------
+
+def logical_to_packed_len(n: int) -> int:
+    """api.py:270-274 / fwd_mainloop.cu:294-303: 15 tokens take 16 slots, a partial group one more."""
+    return (n // 15) * 16 + (0 if n % 15 == 0 else 1 + n % 15)
+
+
+def packed_len_to_logical(n: int) -> int:
+    """fwd_mainloop.cu:283-292."""
+    return (n // 16) * 15 + (0 if n % 16 == 0 else n % 16 - 1)
+
+
+def pack_k(k_s: torch.Tensor):
+    """api.py:122-149 (quant_block_size 16).  k_s: smoothed K [B,H,N,D] bf16.  Per group of 15 tokens
+    (the last one zero-padded): slot 0 = the FP4-rounded group mean, slots 1..15 = k - lambda * mean
+    with lambda = <k, mean> / |mean|^2.  Returns (packed [B,H,16*G,D] in k's dtype, lambda fp32
+    [B,H,16*G], 0 in the mean slots)."""
+    B, H, _, D = k_s.shape
+    x = pad_tokens(k_s, 15)
+    G = x.shape[-2] // 15
+    xb = x.reshape(B, H, G, 15, D)
+    mean = xb.mean(dim=-2)                                                    # bf16 result, fp32 accumulate
+    mean = torch.from_numpy(nvfp4.fake_quant(mean.float().numpy())).to(k_s.dtype)   # round_to_blockscaled_fp4
+    mf = mean.float()
+    nsq = (mf * mf).sum(dim=-1, keepdim=True)
+    direction = torch.where(nsq > 0, mf / nsq, torch.zeros_like(mf))
+    lamb = torch.einsum("bhnmd,bhnd->bhnm", xb.float(), direction)
+    res = (xb.float() - lamb.unsqueeze(-1) * mf.unsqueeze(-2)).to(k_s.dtype)
+    lamb = torch.cat([torch.zeros(B, H, G, 1), lamb.float()], dim=-1)
+    packed = torch.cat([mean.unsqueeze(-2), res], dim=-2)
+    return packed.reshape(B, H, G * 16, D), lamb.reshape(B, H, G * 16)
+
+
+def pack_v(v: torch.Tensor):
+    """api.py:150-177 with split_first=False: a zero row in every mean slot."""
+    B, H, _, D = v.shape
+    x = pad_tokens(v, 15)
+    G = x.shape[-2] // 15
+    xb = x.reshape(B, H, G, 15, D)
+    packed = torch.cat([torch.zeros(B, H, G, 1, D, dtype=v.dtype), xb], dim=-2)
+    return packed.reshape(B, H, G * 16, D)
+
+
+def sageattn4_emulated(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool = False,
+                       sm_scale: float | None = None, mode: str = "exact"):
+    """The fork's K-packing pipeline (api.py:179-205, 250-288) with per_block_mean=True and
+    v_trick=False, on HND bf16 CPU tensors."""
+    D = q.shape[-1]
+    Lq, Lk = q.shape[-2], k.shape[-2]
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    g = q.shape[1] // k.shape[1]
+    k_s, _ = smooth_k(k)
+    q_s, qm = q_block_mean(pad_tokens(q))
+    k_p, lamb = pack_k(k_s)
+    v_p = pack_v(v)
+    k_p = pad_tokens(k_p)
+    lamb = pad_tokens(lamb.unsqueeze(-1)).squeeze(-1)
+    k_rep = k_p.repeat_interleave(g, dim=1) if g > 1 else k_p
+    delta_s = torch.matmul(qm, k_rep.transpose(-2, -1)).to(torch.float32)     # from the unrounded packed K
+    qd = dequant(*quant_rows(q_s, mode))
+    kd = dequant(*quant_rows(k_p, mode))
+    vtd = dequant(*quant_v_transposed(pad_tokens(v_p), mode))
+    out = attention_quantised(qd, kd, vtd, delta_s, Lq, logical_to_packed_len(Lk), sm_scale, is_causal, lamb=lamb)
+    return out.to(q.dtype)
 
 
 def sdpa_fp32(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool = False,

@@ -10,6 +10,10 @@ Outputs:
 
 * ``quant_emulation.npz``  - seeded inputs (bf16 bit patterns) incl. every E2M1 tie point, and the
   reference emulation's de-quantised result for row-wise and token-wise (transposed V) blocks.
+* ``pack_emulation.npz`` - the fork's K-packing preprocessing (``preprocess_qkv``, api.py:112-205, run
+  unchanged on CPU with per_block_mean=True; its Triton group-mean helper, which needs a GPU, is
+  replaced by the same arithmetic in PyTorch): packed K, lambda, packed V and delta_s for a seeded
+  ragged input and for the s128 real-activation fixture.
 * ``llama_fixture_qkv.npz`` - the reference's real-activation test inputs
   (``tests/fixtures/llama3p1_8b_instruct_l16_h30_s256_qkv.pt`` and ``..._h15_s128_qkv.pt``; inputs
   only, the reference commits no expected outputs) as bf16 bit patterns, plus the reference
@@ -26,11 +30,12 @@ import torch
 HERE = Path(__file__).resolve().parent
 
 
-def lift(api_path: Path, names):
+def lift(api_path: Path, names, extra=None):
     tree = ast.parse(api_path.read_text())
     body = [n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name in names]
     mod = ast.Module(body=body, type_ignores=[])
     ns = {"torch": torch}
+    ns.update(extra or {})
     exec(compile(mod, str(api_path), "exec"), ns)
     return [ns[n] for n in names]
 
@@ -77,6 +82,32 @@ def main(ref_root: str):
         out[f"{tag}_v_fq"] = bits(rttb(v))
         sd = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float())
         out[f"{tag}_sdpa"] = sd.numpy()
+    # ---- K-packing preprocessing (api.py:112-205), executed unchanged
+    import einops
+    from typing import Tuple
+
+    def group_mean(q):                     # stands in for triton_group_mean (api.py:26-72): fp32 mean per 128 tokens
+        B, H, L, D = q.shape
+        g = q.float().reshape(B, H, L // 128, 128, D)
+        mean = g.sum(dim=-2) / 128
+        return (g - mean.unsqueeze(-2)).to(q.dtype).reshape(B, H, L, D), mean.to(q.dtype)
+
+    (pre,) = lift(ref / "sageattn4" / "api.py", ["preprocess_qkv"],
+                  {"E": einops, "F": torch.nn.functional, "Tuple": Tuple, "round_to_blockscaled_fp4": rtb,
+                   "round_to_token_blockscaled_fp4": rttb, "triton_group_mean": group_mean})
+    pk = {}
+    g2 = torch.Generator().manual_seed(7)
+    qs = torch.randn(1, 2, 70, 64, generator=g2).to(torch.bfloat16)
+    ks_ = (torch.randn(1, 2, 100, 64, generator=g2) + 1.5 * torch.randn(1, 2, 1, 64, generator=g2)).to(torch.bfloat16)
+    vs = torch.randn(1, 2, 100, 64, generator=g2).to(torch.bfloat16)
+    d128 = torch.load(ref / "tests" / "fixtures" / "llama3p1_8b_instruct_l16_h15_s128_qkv.pt", map_location="cpu")
+    for tag, (q, k, v) in {"rand": (qs, ks_, vs), "s128": (d128["q"], d128["k"], d128["v"])}.items():
+        qp, kp, vp, ds, lam = pre(q.clone(), k.clone(), v.clone(), True, 16, None)
+        pk[f"{tag}_q"], pk[f"{tag}_k"], pk[f"{tag}_v"] = bits(q), bits(k), bits(v)
+        pk[f"{tag}_kp"], pk[f"{tag}_vp"] = bits(kp), bits(vp)
+        pk[f"{tag}_lam"], pk[f"{tag}_ds"] = lam.float().numpy(), ds.float().numpy()
+    np.savez_compressed(HERE / "pack_emulation.npz", **pk)
+    print("pack_emulation.npz", {k_: v_.shape for k_, v_ in pk.items()})
     np.savez_compressed(HERE / "llama_fixture_qkv.npz", **out)
     print("llama_fixture_qkv.npz", {k_: v_.shape for k_, v_ in out.items()})
 

@@ -83,3 +83,25 @@ def test_ref_sf_swizzle_roundtrip():
     perm = nvfp4.ref_k_row_permutation()
     assert sorted(perm.tolist()) == list(range(128))
     assert perm[:10].tolist() == [0, 1, 8, 9, 16, 17, 24, 25, 2, 3]
+
+
+@pytest.mark.parametrize("tag", ["rand", "s128"])
+def test_k_packing_matches_reference_preprocessing(tag):
+    """oracle.sage3.pack_k / pack_v / delta_s against the fork's own preprocess_qkv (api.py:112-205,
+    per_block_mean=True), run unchanged on CPU by tests/golden/make_golden.py."""
+    z = np.load(G / "pack_emulation.npz")
+    bf = lambda name: torch.from_numpy(f32(z[f"{tag}_{name}"])).to(torch.bfloat16)
+    q, k, v = bf("q"), bf("k"), bf("v")
+    k_s, _ = sage3.smooth_k(k)
+    kp, lam = sage3.pack_k(k_s)
+    kp, lam = sage3.pad_tokens(kp), sage3.pad_tokens(lam.unsqueeze(-1)).squeeze(-1)
+    vp = sage3.pad_tokens(sage3.pack_v(v))
+    assert kp.shape == tuple(z[f"{tag}_kp"].shape) and sage3.logical_to_packed_len(k.shape[-2]) <= kp.shape[-2]
+    assert torch.equal(vp, bf("vp"))
+    assert torch.equal(kp, bf("kp"))
+    np.testing.assert_allclose(lam.numpy(), z[f"{tag}_lam"], rtol=1e-6, atol=1e-7)
+    _, qm = sage3.q_block_mean(sage3.pad_tokens(q))
+    ds = torch.matmul(qm, kp.transpose(-2, -1)).float()
+    np.testing.assert_allclose(ds.numpy(), z[f"{tag}_ds"], rtol=1e-6, atol=1e-6)
+    for n in (0, 1, 14, 15, 16, 29, 30, 100, 32760):
+        assert sage3.packed_len_to_logical(sage3.logical_to_packed_len(n)) == n
