@@ -18,6 +18,8 @@
  *   sage3_attn_fwd    <- blackwell/api.cpp:258-395 mha_fwd (pybind name "fwd", :399-405)
  *   sage3_attention   <- api.py:250-288 sageattn4_blackwell without its K-packing steps
  *                        (= the SageAttention3 call sequence), in one call
+ *   sage3_pack_kv, sage3_attn_fwd_packed <- the K-packing steps themselves (api.py:122-177, 267-274;
+ *                        kernel side fwd_mainloop.cu:796-891)
  *
  * Tensor arguments are bf16 with the last (head_dim) dimension contiguous; batch / head / token
  * strides are given in elements, so both the "HND" [B,H,N,D] and "NHD" [B,N,H,D] layouts of
@@ -127,6 +129,23 @@ typedef struct {
                                 workspace is used and cannot be read back by the caller              */
 } sage3_fwd_args;
 
+/* K-packing mode of the fork ("SageAttention4", api.py:122-177, 193-203): every 15 key tokens become 16 key
+ * slots - the FP4-rounded group mean and 15 residuals k - lambda * mean - and V gets a zero row in every
+ * mean slot. */
+typedef struct {
+  sage3_shape shape;         /* B, Hkv, Nk (key tokens), D are used                                  */
+  sage3_tensor k, v;         /* v.ptr may be NULL                                                    */
+  int32_t smooth_k;          /* 1: remove the K channel means first (api.py:184)                     */
+  const void* km_in;         /* optional bf16 [B,Hkv,D]: use these means instead of computing them   */
+  void* km;                  /* out: the means, when smooth_k and km_in == NULL                      */
+  void* k_packed;            /* out bf16 [B,Hkv,sage3_packed_rows(Nk),D]                             */
+  void* v_packed;            /* out bf16, same shape (needed when v.ptr != NULL)                     */
+  float* k_lambda;           /* out fp32 [B,Hkv,ceil(sage3_packed_rows(Nk)/128)*128], 0 in mean slots
+                                and padding                                                          */
+  void* scratch;             /* as in sage3_quant_args (only used when the means are computed here)  */
+  size_t scratch_bytes;
+} sage3_pack_args;
+
 SAGE3_API int sage3_version(void);
 SAGE3_API const char* sage3_status_string(int status);
 /* cudaError_t of the most recent failing CUDA call made by this thread inside the library. */
@@ -137,6 +156,15 @@ SAGE3_API int sage3_buffer_sizes(const sage3_shape* shape, int per_block_mean, s
 SAGE3_API int sage3_quant_qkv(const sage3_quant_args* args, void* stream);
 SAGE3_API int sage3_attn_fwd(const sage3_attn_args* args, void* stream);
 SAGE3_API int sage3_attention(const sage3_fwd_args* args, void* stream);
+/* K-packing mode.  sage3_pack_kv replaces quant_pack_k / quant_pack_v and the K centring of api.py:122-177,
+ * 184, 193-194 (eager PyTorch in the reference); its outputs go through sage3_quant_qkv with
+ * shape.Nk = sage3_packed_rows(Nk) and smooth_k = 0.  sage3_attn_fwd_packed is sage3_attn_fwd with the
+ * lambda correction, slot masking and packed causal mask of fwd_mainloop.cu:273-324, 796-891 (per-block-mean
+ * variant); args->shape.Nk must be sage3_packed_len(Nk), the number of occupied key slots (api.py:267-274). */
+SAGE3_API int sage3_packed_rows(int nk);   /* 16 * ceil(nk / 15): rows of the packed tensors                */
+SAGE3_API int sage3_packed_len(int nk);    /* occupied slots: 16 per full group, tokens + 1 for a partial one */
+SAGE3_API int sage3_pack_kv(const sage3_pack_args* args, void* stream);
+SAGE3_API int sage3_attn_fwd_packed(const sage3_attn_args* args, const float* k_lambda, void* stream);
 
 /* K channel means (bf16 [B,Hkv,D] into km_out; shape->Hq and shape->Nq are ignored) for callers that
  * cannot allocate device memory where they run - for example a server that gave all device memory to

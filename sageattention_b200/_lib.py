@@ -59,9 +59,16 @@ class FwdArgs(C.Structure):
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("device_status", C.c_void_p)]
 
 
+class PackArgs(C.Structure):
+    _fields_ = [("shape", Shape), ("k", Tensor), ("v", Tensor), ("smooth_k", C.c_int32),
+                ("km_in", C.c_void_p), ("km", C.c_void_p), ("k_packed", C.c_void_p), ("v_packed", C.c_void_p),
+                ("k_lambda", C.c_void_p), ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t)]
+
+
 EXPORTS = ("sage3_version", "sage3_status_string", "sage3_last_cuda_error", "sage3_buffer_sizes",
            "sage3_quant_qkv", "sage3_attn_fwd", "sage3_attention", "sage3_read_device_status",
-           "sage3_k_mean_static")
+           "sage3_k_mean_static", "sage3_packed_rows", "sage3_packed_len", "sage3_pack_kv",
+           "sage3_attn_fwd_packed")
 
 _lib = None
 
@@ -85,6 +92,10 @@ def load() -> C.CDLL:
     lib.sage3_attention.argtypes = [C.POINTER(FwdArgs), C.c_void_p]
     lib.sage3_read_device_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
     lib.sage3_k_mean_static.argtypes = [C.POINTER(Shape), C.POINTER(Tensor), C.c_void_p, C.c_void_p]
+    lib.sage3_packed_rows.argtypes = [C.c_int]
+    lib.sage3_packed_len.argtypes = [C.c_int]
+    lib.sage3_pack_kv.argtypes = [C.POINTER(PackArgs), C.c_void_p]
+    lib.sage3_attn_fwd_packed.argtypes = [C.POINTER(AttnArgs), C.c_void_p, C.c_void_p]
     for name in EXPORTS:
         getattr(lib, name)            # raises AttributeError if an export is missing
     _lib = lib

@@ -7,6 +7,8 @@ Mirrors the reference's operator interface:
   ``Hq % Hkv == 0``, default scale ``D**-0.5``, optional log-sum-exp output);
 * ``sageattn3_blackwell(q, k, v, ...)`` - the FP4 operator of
   ``sageattention3_blackwell/sageattn4/api.py:250-288`` without the fork's K-packing steps;
+* ``sageattn4_blackwell(q, k, v, ...)`` - the same operator with the K-packing steps (15 tokens -> group
+  mean + 15 residuals, ``api.py:122-177,267-274``);
 * ``sageattn_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, ...)`` - ``sageattention/core.py:334-448``.
 
 All tensor work happens in ``libsage3_b200.so`` (hand-written sm_100a CUDA behind a C ABI); this
@@ -81,6 +83,8 @@ class QuantizedQKV:
     km: Optional[torch.Tensor]
     delta_s: Optional[torch.Tensor]
     delta_s_rows: int
+    k_lambda: Optional[torch.Tensor] = None          # K-packing mode: fp32 [B,Hkv,Tk*128]
+    nk_slots: Optional[int] = None                   # K-packing mode: occupied key slots (<= Nk)
 
 
 def quantize_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",
@@ -173,10 +177,74 @@ def fp4_attention(qz: QuantizedQKV, sm_scale: Optional[float] = None, is_causal:
     a.sm_scale, a.is_causal = float(sm_scale), int(bool(is_causal))
     a.device_status = status.data_ptr()
     with torch.cuda.device(dev):
-        _lib.check(lib.sage3_attn_fwd(C.byref(a), _stream_ptr(dev)), "sage3_attn_fwd")
+        if qz.k_lambda is not None:
+            a.shape = _lib.Shape(B, Hq, Hkv, Nq, int(qz.nk_slots), D)
+            _lib.check(lib.sage3_attn_fwd_packed(C.byref(a), qz.k_lambda.data_ptr(), _stream_ptr(dev)),
+                       "sage3_attn_fwd_packed")
+        else:
+            _lib.check(lib.sage3_attn_fwd(C.byref(a), _stream_ptr(dev)), "sage3_attn_fwd")
         if check_status:
             _lib.check(lib.sage3_read_device_status(status.data_ptr(), _stream_ptr(dev), None), "attention kernel")
     return (out, lse) if return_lse else out
+
+
+def pack_kv(k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND", smooth_k: bool = True):
+    """K-packing preprocessing (``quant_pack_k`` / ``quant_pack_v`` and the K centring of
+    ``sageattn4/api.py:122-177,184``): every 15 key tokens become 16 slots (FP4-rounded group mean + 15
+    residuals), V gets a zero row per mean slot.  Returns ``(k_packed, v_packed, k_lambda, km)`` with the
+    packed tensors in HND ``[B,Hkv,16*ceil(Nk/15),D]`` and ``k_lambda`` fp32 padded to a multiple of 128."""
+    lib = _lib.load()
+    _check_device(k)
+    B, Hkv, Nk, D, ksb, ksh, ksn = _as_bhnd_strides(k, tensor_layout)
+    Bv, Hv, Nv, Dv, vsb, vsh, vsn = _as_bhnd_strides(v, tensor_layout)
+    if (B, Hkv, Nk, D) != (Bv, Hv, Nv, Dv):
+        raise ValueError("k and v shapes do not match")
+    dev = k.device
+    rows = lib.sage3_packed_rows(Nk)
+    kp = torch.empty((B, Hkv, rows, D), dtype=torch.bfloat16, device=dev)
+    vp = torch.empty((B, Hkv, rows, D), dtype=torch.bfloat16, device=dev)
+    lam = torch.empty((B, Hkv, (rows + 127) // 128 * 128), dtype=torch.float32, device=dev)
+    km = torch.empty((B, Hkv, D), dtype=torch.bfloat16, device=dev) if smooth_k else None
+    z = buffer_sizes(B, Hkv, Hkv, Nk, Nk, D, 1)
+    scratch = torch.empty(max(int(z.scratch), 256), dtype=torch.uint8, device=dev)
+    a = _lib.PackArgs()
+    a.shape = _lib.Shape(B, Hkv, Hkv, Nk, Nk, D)
+    a.k, a.v = _tensor_arg(k, ksb, ksh, ksn), _tensor_arg(v, vsb, vsh, vsn)
+    a.smooth_k = int(smooth_k)
+    a.km = km.data_ptr() if km is not None else None
+    a.k_packed, a.v_packed, a.k_lambda = kp.data_ptr(), vp.data_ptr(), lam.data_ptr()
+    a.scratch, a.scratch_bytes = scratch.data_ptr(), scratch.numel()
+    with torch.cuda.device(dev):
+        _lib.check(lib.sage3_pack_kv(C.byref(a), _stream_ptr(dev)), "sage3_pack_kv")
+    return kp, vp, lam, km
+
+
+def sageattn4_blackwell(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",
+                        is_causal: bool = False, sm_scale: Optional[float] = None, per_block_mean: bool = True,
+                        quant_block: int = 16, v_trick: Optional[bool] = None, attn_mask=None,
+                        check_status: bool = False, **kwargs):
+    """The fork's K-packing operator (``sageattn4_blackwell``, ``sageattn4/api.py:250-288``): K is centred,
+    packed 15 -> 16 (group mean + residuals) and the kernel restores every score as
+    ``q.residual + lambda * q.mean``.  Supported: ``quant_block=16``, ``per_block_mean=True`` and the V layout
+    that goes with it (``v_trick`` False, a zero row per mean slot)."""
+    lib = _lib.load()
+    if attn_mask is not None:
+        raise NotImplementedError("attn_mask is not supported (the reference ignores it, api.py:250)")
+    if quant_block != 16:
+        raise AssertionError("quant_block must be 16")                                   # api.py:251
+    if not per_block_mean or v_trick:
+        raise NotImplementedError("the K-packing mode is built for per_block_mean=True / v_trick=False")
+    if q.shape[-1] not in (64, 128):
+        raise ValueError(f"Unsupported Headdim {q.shape[-1]}")
+    kp, vp, lam, _ = pack_kv(k, v, tensor_layout, smooth_k=True)
+    if tensor_layout == "NHD":
+        kp, vp = kp.transpose(1, 2), vp.transpose(1, 2)          # views; the quantiser takes strides
+    qz = quantize_qkv(q, kp, vp, tensor_layout, per_block_mean=True, smooth_k=False)
+    qz.k_lambda = lam
+    Nk = k.shape[2] if tensor_layout == "HND" else k.shape[1]
+    qz.nk_slots = lib.sage3_packed_len(Nk)
+    return fp4_attention(qz, sm_scale=sm_scale, is_causal=is_causal, tensor_layout=tensor_layout,
+                         check_status=check_status)
 
 
 def sageattn3_blackwell(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",

@@ -79,7 +79,9 @@ struct Smem {
   static constexpr int zero = b1 + kStages * 2 * 2048;    // second K chunk of every rank-1 operand; it must lie
                                                           // ABOVE them: the descriptor offset to it is unsigned
   static constexpr int dsraw = zero + 2048;               // [kStages][2][256] delta_s rows as loaded
-  static constexpr int stats = dsraw + kStages * 2 * 256; // [2][8 blocks][128 rows] float2 (exponent offset, scale)
+  static constexpr int lam = dsraw + kStages * 2 * 256;   // [kStages][128] f32: lambda of the key slots (K-packing mode),
+                                                          // loaded and released with the V stage
+  static constexpr int stats = lam + kStages * 512;       // [2][8 blocks][128 rows] float2 (exponent offset, scale)
   static constexpr int bars = stats + 2 * 8 * 128 * 8;
   static constexpr int total = bars + 512;
 };
@@ -111,6 +113,8 @@ struct KParams {
   int64_t o_sb, o_sh, o_sn;
   int B, Hq, Hkv, Nq, Nk, Tq, Tk, ds_rows;
   float scale_log2;      // sm_scale * log2(e)
+  const float* lam;      // K-packing mode: lambda per key slot, fp32 [B,Hkv,Tk*128]; Nk is the packed length
+  int Nk_log;            // number of key tokens (= Nk unless packed)
 };
 
 // Bounded wait on an mbarrier phase; also gives up as soon as any CTA has reported a failure.  A failing poll
@@ -163,9 +167,25 @@ __device__ __forceinline__ float max16(const uint32_t* r) {
 //   st        this thread's column of the shared scratch: per block (exponent offset, scale)
 // Pass 1: block maxima -> new row maximum, rescale factor alpha = 2^((m_old - m_new) * c) (returned),
 // per-block scales (P blockmax / 6) as E4M3 bytes for the PV MMA (`sfp`) and, unrounded, in `st`.
-template <bool kMask>
+// K-packing mode (fwd_mainloop.cu:796-845, 878-881): a block of 16 keys is one group - slot 0 holds the
+// score of the group mean, which every other score of the group gets added lambda times; the slot itself
+// carries no token and is masked out.
+__device__ __forceinline__ void apply_lambda(uint32_t (&r)[16], const float* lam16) {
+  const float s0 = __uint_as_float(r[0]);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float4 l4 = *reinterpret_cast<const float4*>(lam16 + 4 * i);
+    if (i > 0) r[4 * i] = __float_as_uint(fmaf(l4.x, s0, __uint_as_float(r[4 * i])));
+    r[4 * i + 1] = __float_as_uint(fmaf(l4.y, s0, __uint_as_float(r[4 * i + 1])));
+    r[4 * i + 2] = __float_as_uint(fmaf(l4.z, s0, __uint_as_float(r[4 * i + 2])));
+    r[4 * i + 3] = __float_as_uint(fmaf(l4.w, s0, __uint_as_float(r[4 * i + 3])));
+  }
+  r[0] = 0xff800000u;
+}
+
+template <bool kMask, bool kPacked>
 __device__ __forceinline__ float softmax_pass1_impl(const uint32_t tm_S, const float c, float& m, float2* st,
-                                                    uint2& sfp, const int n0, const int key_lim) {
+                                                    uint2& sfp, const int n0, const int key_lim, const float* lam_s) {
   uint32_t ra[16], rb[16];
   float bm[8];
   tmem_ld16(tm_S, ra);
@@ -173,6 +193,7 @@ __device__ __forceinline__ float softmax_pass1_impl(const uint32_t tm_S, const f
   for (int blk = 0; blk < 8; blk += 2) {
     tmem_wait_ld();
     tmem_ld16(tm_S + (blk + 1) * 16, rb);
+    if (kPacked) apply_lambda(ra, lam_s + blk * 16);
     if (kMask) {
 #pragma unroll
       for (int i = 0; i < 16; ++i) ra[i] = (n0 + blk * 16 + i > key_lim) ? 0xff800000u : ra[i];
@@ -180,6 +201,7 @@ __device__ __forceinline__ float softmax_pass1_impl(const uint32_t tm_S, const f
     bm[blk] = max16(ra);
     tmem_wait_ld();
     if (blk + 2 < 8) tmem_ld16(tm_S + (blk + 2) * 16, ra);
+    if (kPacked) apply_lambda(rb, lam_s + (blk + 1) * 16);
     if (kMask) {
 #pragma unroll
       for (int i = 0; i < 16; ++i) rb[i] = (n0 + (blk + 1) * 16 + i > key_lim) ? 0xff800000u : rb[i];
@@ -205,10 +227,10 @@ __device__ __forceinline__ float softmax_pass1_impl(const uint32_t tm_S, const f
 
 // Pass 2: P / blockscale = 2^(s*c - (bm*c + log2(1/6))) in [0, 6] -> E2M1 codes into the swizzled P^ tile;
 // the row sum uses the unrounded values times the unrounded block scale (softmax_fused.h:135-153).
-template <bool kMask>
+template <bool kMask, bool kPacked>
 __device__ __forceinline__ void softmax_pass2_impl(const uint32_t tm_S, const float c, const float alpha, float& l,
                                                    const float2* st, uint8_t* p_row, const int swz, const int n0,
-                                                   const int key_lim) {
+                                                   const int key_lim, const float* lam_s) {
   uint32_t ra[16], rb[16];
   const float2 c2 = make_float2(c, c);
   float lsum = 0.f;
@@ -222,6 +244,7 @@ __device__ __forceinline__ void softmax_pass2_impl(const uint32_t tm_S, const fl
     tmem_wait_ld();
     if (blk < 7) tmem_ld16(tm_S + (blk + 1) * 16, rn);
     const float2 ns_next = st[((blk + 1) & 7) * 128];
+    if (kPacked) apply_lambda(r, lam_s + blk * 16);
     if (kMask) {
 #pragma unroll
       for (int i = 0; i < 16; ++i) r[i] = (n0 + blk * 16 + i > key_lim) ? 0xff800000u : r[i];
@@ -246,14 +269,23 @@ __device__ __forceinline__ void softmax_pass2_impl(const uint32_t tm_S, const fl
 
 // Tiles that need the key-padding / causal mask are rare (the last key tile, the diagonal) and go
 // through real calls so that their extra selects do not cost the hot path registers.
+template <bool kPacked>
 __device__ __noinline__ float softmax_pass1_masked(const uint32_t tm_S, const float c, float& m, float2* st,
-                                                   uint2& sfp, const int n0, const int key_lim) {
-  return softmax_pass1_impl<true>(tm_S, c, m, st, sfp, n0, key_lim);
+                                                   uint2& sfp, const int n0, const int key_lim, const float* lam_s) {
+  return softmax_pass1_impl<true, kPacked>(tm_S, c, m, st, sfp, n0, key_lim, lam_s);
 }
+template <bool kPacked>
 __device__ __noinline__ void softmax_pass2_masked(const uint32_t tm_S, const float c, const float alpha, float& l,
                                                   const float2* st, uint8_t* p_row, const int swz, const int n0,
-                                                  const int key_lim) {
-  softmax_pass2_impl<true>(tm_S, c, alpha, l, st, p_row, swz, n0, key_lim);
+                                                  const int key_lim, const float* lam_s) {
+  softmax_pass2_impl<true, kPacked>(tm_S, c, alpha, l, st, p_row, swz, n0, key_lim, lam_s);
+}
+
+// K-packing mode: 15 tokens occupy 16 key slots (fwd_mainloop.cu:273-303).  Last slot that token `tok` or an
+// earlier one occupies / number of slots the first `len` tokens occupy.
+__device__ __forceinline__ int packed_slot_of_token(const int tok) { return (tok / 15) * 16 + tok % 15 + 1; }
+__device__ __forceinline__ int packed_len_of(const int len) {
+  return len <= 0 ? 0 : (len / 15) * 16 + (len % 15 == 0 ? 0 : len % 15 + 1);
 }
 
 // One unit of work of a CTA: two adjacent query tiles of one head.
@@ -271,7 +303,7 @@ __device__ __forceinline__ int work_at(const int r, const int total) {
   return w < total ? w : -1;
 }
 
-template <bool kCausal>
+template <bool kCausal, bool kPacked>
 __device__ __forceinline__ Work get_work(const KParams& P, const int w) {
   Work k;
   const int n_pairs = (P.Tq + 1) >> 1;
@@ -298,7 +330,8 @@ __device__ __forceinline__ Work get_work(const KParams& P, const int w) {
       n = P.Tk;
       if (kCausal) {
         const int q_end = min((qt + 1) * kBlockM, P.Nq);
-        const int lim = q_end + P.Nk - P.Nq;               // keys [0, lim) can be visible
+        int lim = q_end + P.Nk_log - P.Nq;                 // key tokens [0, lim) can be visible
+        if (kPacked) lim = packed_len_of(lim);             // ... which occupy this many key slots
         n = lim <= 0 ? 0 : min(P.Tk, (lim + kBlockN - 1) / kBlockN);
       }
     }
@@ -308,7 +341,7 @@ __device__ __forceinline__ Work get_work(const KParams& P, const int w) {
   return k;
 }
 
-template <int D, bool kCausal>
+template <int D, bool kCausal, bool kPacked>
 __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                                                                    const __grid_constant__ CUtensorMap tm_k,
                                                                    const __grid_constant__ CUtensorMap tm_v,
@@ -387,7 +420,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         uint32_t qn[2] = {0, 0};              // Q tiles loaded so far per slot
         bool ok = true;
         for (int r = 0, w; ok && (w = work_at(r, total_work)) >= 0; ++r) {
-          const Work wk = get_work<kCausal>(P, w);
+          const Work wk = get_work<kCausal, kPacked>(P, w);
           int64_t ds_row[2];
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
@@ -423,9 +456,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
             ++gk;
             if (!(ok = wait_bar<false>(bars + Bars::v_empty + 8 * s, ph, abort_s, P.status, 11))) break;
             const uint32_t vb = bars + Bars::v_full + 8 * s;
-            mbar_arrive_expect_tx(vb, L::kVBytes + L::kSfV);
+            mbar_arrive_expect_tx(vb, L::kVBytes + L::kSfV + (kPacked ? 512 : 0));
             tma_load_2d(sbase + L::v + s * L::kVBytes, &tm_v, 0, (int)((kvhead + j) * D), vb);
             bulk_load(sbase + L::sfv + s * 1024, P.vt_sf + (kvhead + j) * L::kSfV, L::kSfV, vb);
+            if (kPacked) bulk_load(sbase + L::lam + s * 512, P.lam + (kvhead + j) * kBlockN, 512, vb);
           }
         }
         if (*abort_s) {
@@ -444,7 +478,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         uint32_t g = 0;
         bool ok = true;
         for (int r = 0, w; ok && (w = work_at(r, total_work)) >= 0; ++r) {
-          const Work wk = get_work<kCausal>(P, w);
+          const Work wk = get_work<kCausal, kPacked>(P, w);
           for (int it = 0; ok && it < wk.n_max; ++it, ++g) {
             const int j = wk.n_max - 1 - it, s = g % kStages;
             if (!(ok = wait_bar<false>(bars + Bars::k_full + 8 * s, (g / kStages) & 1, abort_s, P.status, 40))) break;
@@ -481,7 +515,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         uint32_t sq[2] = {0, 0};              // QK groups issued so far per tile slot (= S_t tiles produced)
         uint32_t qn[2] = {0, 0};              // Q tiles taken so far per slot
         for (int r = 0, w; ok && (w = work_at(r, total_work)) >= 0; ++r) {
-          const Work wk = get_work<kCausal>(P, w);
+          const Work wk = get_work<kCausal, kPacked>(P, w);
           for (int it = 0; ok && it < wk.n_max; ++it, ++g) {
             const int j = wk.n_max - 1 - it, s = g % kStages;
             const uint32_t ph = (g / kStages) & 1;
@@ -542,7 +576,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         bool ok = true;
         uint32_t g = 0, pv_cnt[2] = {0, 0}, pv_total = 0;
         for (int r = 0, w; ok && (w = work_at(r, total_work)) >= 0; ++r) {
-          const Work wk = get_work<kCausal>(P, w);
+          const Work wk = get_work<kCausal, kPacked>(P, w);
           for (int it = 0; ok && it < wk.n_max; ++it, ++g) {
             const int j = wk.n_max - 1 - it, s = g % kStages;
             const bool act1 = j < wk.n_t[1];
@@ -591,10 +625,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       const uint32_t bar_s = bars + Bars::s_full + 8 * t, bar_p = bars + Bars::p_full + 8 * t;
       const uint32_t bar_o = bars + Bars::o_full + 8 * t;
       uint32_t sc = 0;                                           // key tiles processed so far by this warpgroup
+      uint32_t g0 = 0;                                           // K/V stages the CTA used before this work item
       bool ok = true;
       for (int r = 0, w; ok && (w = work_at(r, total_work)) >= 0; ++r) {
-        const Work wk = get_work<kCausal>(P, w);
+        const Work wk = get_work<kCausal, kPacked>(P, w);
         const int n_mine = wk.n_t[t];
+        const uint32_t g_first = g0 + (uint32_t)(wk.n_max - n_mine);   // stage counter of this tile's first key tile
+        g0 += (uint32_t)wk.n_max;
         const int qt = 2 * wk.pair + t;
         const int q0 = qt * kBlockM, qpos = q0 + row;
         __nv_bfloat16* orow = P.out + wk.b * P.o_sb + wk.hq * P.o_sh + (int64_t)qpos * P.o_sn;
@@ -607,7 +644,15 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           }
           continue;
         }
-        const int key_lim = min(P.Nk - 1, kCausal ? qpos + P.Nk - P.Nq : 0x7fffffff);   // last visible key
+        // last visible key (slot): key padding, and the bottom-right aligned causal diagonal - in K-packing mode
+        // the slots of the tokens up to the diagonal one
+        auto causal_limit = [&](const int qp) {
+          const int tok = qp + P.Nk_log - P.Nq;                  // last visible key token
+          if (!kPacked) return tok;
+          return tok < 0 ? -1 : packed_slot_of_token(tok);
+        };
+        const int key_lim = min(P.Nk - 1, kCausal ? causal_limit(qpos) : 0x7fffffff);
+        const int first_row_lim = kCausal ? causal_limit(q0) : 0x7fffffff;
         float2 O2[D / 2];
 #pragma unroll
         for (int i = 0; i < D / 2; ++i) O2[i] = make_float2(0.f, 0.f);
@@ -616,16 +661,24 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         for (int it = 0; it < n_mine; ++it, ++sc) {
           const int j = n_mine - 1 - it;
           const int n0 = j * kBlockN;
-          const bool need_mask = (n0 + kBlockN - 1 >= P.Nk) || (kCausal && n0 + kBlockN - 1 > q0 + P.Nk - P.Nq);
+          const bool need_mask = (n0 + kBlockN - 1 >= P.Nk) || (kCausal && n0 + kBlockN - 1 > first_row_lim);
+          const float* lam_s = nullptr;
+          if (kPacked) {
+            // lambda of this key tile travels with its V stage (released only after both tiles' P.V MMAs, i.e.
+            // after every reader here is done); the stage has normally landed long before
+            const uint32_t g = g_first + (uint32_t)it;
+            if (!(ok = wait_bar<false>(bars + Bars::v_full + 8 * (g % kStages), (g / kStages) & 1, abort_s, P.status, 33))) break;
+            lam_s = reinterpret_cast<const float*>(smem + L::lam) + (g % kStages) * 128;
+          }
           if (!(ok = wait_bar<false>(bar_s, sc & 1, abort_s, P.status, 30))) break;
           tc_fence_after();
           uint2 sfp;
-          const float alpha = need_mask ? softmax_pass1_masked(tm_S, c, m, st, sfp, n0, key_lim)
-                                        : softmax_pass1_impl<false>(tm_S, c, m, st, sfp, 0, 0);
+          const float alpha = need_mask ? softmax_pass1_masked<kPacked>(tm_S, c, m, st, sfp, n0, key_lim, lam_s)
+                                        : softmax_pass1_impl<false, kPacked>(tm_S, c, m, st, sfp, 0, 0, lam_s);
           sfp_row[0] = sfp.x;
           sfp_row[128] = sfp.y;
-          if (need_mask) softmax_pass2_masked(tm_S, c, alpha, l, st, p_row, swz, n0, key_lim);
-          else softmax_pass2_impl<false>(tm_S, c, alpha, l, st, p_row, swz, 0, 0);
+          if (need_mask) softmax_pass2_masked<kPacked>(tm_S, c, alpha, l, st, p_row, swz, n0, key_lim, lam_s);
+          else softmax_pass2_impl<false, kPacked>(tm_S, c, alpha, l, st, p_row, swz, 0, 0, lam_s);
           // S consumed and P^ written: hand both to the MMA issuers
           tc_fence_before();
           fence_proxy_async_smem();
@@ -720,7 +773,7 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint32_t row_byte
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int D, bool kCausal>
+template <int D, bool kCausal, bool kPacked>
 cudaError_t launch(const AttnArgs& a, cudaStream_t stream) {
   using L = Smem<D>;
   const int Tq = (a.Nq + 127) / 128, Tk = (a.Nk + 127) / 128;
@@ -736,7 +789,10 @@ cudaError_t launch(const AttnArgs& a, cudaStream_t stream) {
   P.o_sb = a.o_sb; P.o_sh = a.o_sh; P.o_sn = a.o_sn;
   P.B = a.B; P.Hq = a.Hq; P.Hkv = a.Hkv; P.Nq = a.Nq; P.Nk = a.Nk; P.Tq = Tq; P.Tk = Tk; P.ds_rows = a.ds_rows;
   P.scale_log2 = a.sm_scale * kLog2e;
-  auto kern = attn_fwd_kernel<D, kCausal>;
+  P.lam = a.k_lambda;
+  // K-packing mode: Nk counts key slots; 16 slots hold 15 tokens, a partial group one slot more than its tokens
+  P.Nk_log = kPacked ? (a.Nk / 16) * 15 + (a.Nk % 16 == 0 ? 0 : a.Nk % 16 - 1) : a.Nk;
+  auto kern = attn_fwd_kernel<D, kCausal, kPacked>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total + 1024);
   if (e != cudaSuccess) return e;
   // persistent CTAs: one per SM (registers and tensor memory allow exactly one), each walks the work list
@@ -752,9 +808,13 @@ cudaError_t launch(const AttnArgs& a, cudaStream_t stream) {
 }  // namespace
 
 cudaError_t launch_attn_fwd(const AttnArgs& a, cudaStream_t stream) {
-  if (a.D == 128) return a.causal ? launch<128, true>(a, stream) : launch<128, false>(a, stream);
-  if (a.D == 64) return a.causal ? launch<64, true>(a, stream) : launch<64, false>(a, stream);
-  return cudaErrorInvalidValue;
+  if (a.D != 128 && a.D != 64) return cudaErrorInvalidValue;
+  if (a.k_lambda) {
+    if (a.D == 128) return a.causal ? launch<128, true, true>(a, stream) : launch<128, false, true>(a, stream);
+    return a.causal ? launch<64, true, true>(a, stream) : launch<64, false, true>(a, stream);
+  }
+  if (a.D == 128) return a.causal ? launch<128, true, false>(a, stream) : launch<128, false, false>(a, stream);
+  return a.causal ? launch<64, true, false>(a, stream) : launch<64, false, false>(a, stream);
 }
 
 }  // namespace sage3

@@ -147,7 +147,7 @@ int sage3_quant_qkv(const sage3_quant_args* a, void* stream_) {
   return SAGE3_OK;
 }
 
-int sage3_attn_fwd(const sage3_attn_args* a, void* stream_) {
+static int attn_fwd_impl(const sage3_attn_args* a, const float* k_lambda, void* stream_) {
   if (a == nullptr) return SAGE3_ERR_ARGUMENT;
   if (int st = check_shape(a->shape)) return st;
   if (!a->q_codes || !a->q_sf || !a->k_codes || !a->k_sf || !a->vt_codes || !a->vt_sf || !a->out || !a->device_status)
@@ -169,7 +169,52 @@ int sage3_attn_fwd(const sage3_attn_args* a, void* stream_) {
   k.lse = a->lse; k.status = a->device_status;
   k.B = s.B; k.Hq = s.Hq; k.Hkv = s.Hkv; k.Nq = s.Nq; k.Nk = s.Nk; k.D = s.D;
   k.sm_scale = a->sm_scale; k.causal = a->is_causal;
+  k.k_lambda = k_lambda;
   e = sage3::launch_attn_fwd(k, stream);
+  if (e != cudaSuccess) return cuda_fail(e);
+  return SAGE3_OK;
+}
+
+int sage3_attn_fwd(const sage3_attn_args* a, void* stream) { return attn_fwd_impl(a, nullptr, stream); }
+
+int sage3_attn_fwd_packed(const sage3_attn_args* a, const float* k_lambda, void* stream) {
+  if (k_lambda == nullptr || !aligned16(k_lambda)) return SAGE3_ERR_ARGUMENT;
+  return attn_fwd_impl(a, k_lambda, stream);
+}
+
+int sage3_packed_rows(int nk) { return nk <= 0 ? 0 : 16 * ((nk + 14) / 15); }
+
+int sage3_packed_len(int nk) { return nk <= 0 ? 0 : (nk / 15) * 16 + (nk % 15 == 0 ? 0 : nk % 15 + 1); }
+
+int sage3_pack_kv(const sage3_pack_args* a, void* stream_) {
+  if (a == nullptr || a->k.ptr == nullptr || a->k_packed == nullptr || a->k_lambda == nullptr) return SAGE3_ERR_ARGUMENT;
+  const sage3_shape& s = a->shape;
+  if (s.B <= 0 || s.Hkv <= 0 || s.Nk <= 0) return SAGE3_ERR_ARGUMENT;
+  if (s.D != 64 && s.D != 128) return SAGE3_ERR_UNSUPPORTED;
+  if (int st = check_tensor(a->k)) return st;
+  if (int st = check_tensor(a->v)) return st;
+  if (a->v.ptr && !a->v_packed) return SAGE3_ERR_ARGUMENT;
+  if (!aligned16(a->k_packed) || !aligned16(a->k_lambda) || (a->v_packed && !aligned16(a->v_packed))) return SAGE3_ERR_ARGUMENT;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const void* km = nullptr;
+  if (a->smooth_k) {
+    if (a->km_in) {
+      km = a->km_in;
+    } else {
+      if (!a->km || !a->scratch || !aligned16(a->scratch)) return SAGE3_ERR_ARGUMENT;
+      if (a->scratch_bytes < sage3::quant_scratch_bytes(s.B, s.Hkv, s.Nk, s.D)) return SAGE3_ERR_ARGUMENT;
+      cudaError_t e = sage3::launch_channel_mean(a->k.ptr, a->k.stride_b, a->k.stride_h, a->k.stride_n, s.B, s.Hkv,
+                                                 s.Nk, s.D, (float)s.Nk, a->scratch, a->km, stream);
+      if (e != cudaSuccess) return cuda_fail(e);
+      km = a->km;
+    }
+  }
+  sage3::PackArgs p{};
+  p.k = a->k.ptr; p.k_sb = a->k.stride_b; p.k_sh = a->k.stride_h; p.k_sn = a->k.stride_n;
+  p.v = a->v.ptr; p.v_sb = a->v.stride_b; p.v_sh = a->v.stride_h; p.v_sn = a->v.stride_n;
+  p.km = km; p.kp = a->k_packed; p.vp = a->v.ptr ? a->v_packed : nullptr; p.lam = a->k_lambda;
+  p.B = s.B; p.Hkv = s.Hkv; p.Nk = s.Nk; p.D = s.D;
+  cudaError_t e = sage3::launch_pack_kv(p, stream);
   if (e != cudaSuccess) return cuda_fail(e);
   return SAGE3_OK;
 }

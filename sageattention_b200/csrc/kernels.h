@@ -24,6 +24,17 @@ cudaError_t launch_quant_qkv(const QuantArgs& a, cudaStream_t stream);
 cudaError_t launch_channel_mean_static(const void* x, int64_t sb, int64_t sh, int64_t sn, int B, int H, int N, int D,
                                        float divisor, void* mean_out, cudaStream_t stream, bool* too_large);
 
+// K-packing mode: 15 tokens -> 16 slots (group mean + residuals), see pack.cu
+struct PackArgs {
+  const void *k, *v;                      // bf16, strides below; v may be null
+  int64_t k_sb, k_sh, k_sn, v_sb, v_sh, v_sn;
+  const void* km;                         // bf16 [B,Hkv,D] K channel means to subtract first, or null
+  void *kp, *vp;                          // bf16 [B,Hkv,16*G,D] contiguous, G = ceil(Nk/15); vp may be null
+  float* lam;                             // fp32 [B,Hkv,ceil(16*G/128)*128]
+  int B, Hkv, Nk, D;
+};
+cudaError_t launch_pack_kv(const PackArgs& a, cudaStream_t stream);
+
 struct DeltaSArgs {
   const void* qm;                         // bf16 [B,Hq,Tq,D]
   const void* k;                          // bf16 raw K, strides below
@@ -45,6 +56,7 @@ struct AttnArgs {
   int B, Hq, Hkv, Nq, Nk, D;
   float sm_scale;
   int causal;
+  const float* k_lambda;                  // K-packing mode: fp32 [B,Hkv,Tk*128]; Nk is then the packed length
 };
 cudaError_t launch_attn_fwd(const AttnArgs& a, cudaStream_t stream);
 

@@ -1,0 +1,104 @@
+"""GPU parity of the K-packing mode ("SageAttention4" of the fork, sageattn4/api.py:122-177, 250-288;
+kernel side fwd_mainloop.cu:273-324, 796-891): the packing kernel against the CPU restatement (which is
+itself pinned to the reference's preprocessing by tests/golden/pack_emulation.npz), the packed attention
+kernel against the oracle run on the very operands the GPU consumed, and the whole operator.
+
+Tolerances.  Packed K residuals and V: bit-exact except where the fp32 summation order of lambda moves a
+value across a bf16 rounding boundary (at most 0.5 % of the elements, each by one bf16 ulp); lambda:
+rel 2e-5.  Attention: cosine >= 0.999 and relative L1 <= 2e-2 against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+import sageattention_b200 as sa
+from oracle import nvfp4, sage3
+from tests import _util as U
+from tests.test_attn_gpu import COS_MIN, REL_L1_MAX
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.mark.parametrize("B,H,N,D", [(1, 2, 100, 64), (1, 2, 128, 128), (2, 3, 333, 128), (1, 1, 15, 128),
+                                     (1, 1, 16, 64), (1, 2, 1, 128), (1, 2, 2000, 128)])
+def test_pack_kernel_matches_oracle(B, H, N, D):
+    _, k, v = U.make_qkv(B, H, H, 8, N, D, seed=N + D, device=DEV)
+    kp, vp, lam, km = sa.pack_kv(k, v)
+    torch.cuda.synchronize()
+    k_s = (k.cpu() - km.cpu().unsqueeze(-2))                       # the K means are checked elsewhere
+    kp_o, lam_o = sage3.pack_k(k_s)
+    vp_o = sage3.pack_v(v.cpu())
+    rows = kp_o.shape[-2]
+    assert kp.shape == (B, H, rows, D) and lam.shape[-1] == (rows + 127) // 128 * 128
+    assert torch.equal(vp.cpu(), vp_o)
+    assert torch.equal(kp.cpu()[:, :, 0::16], kp_o[:, :, 0::16])  # the FP4-rounded group means: exact
+    np.testing.assert_allclose(lam.cpu()[..., :rows].numpy(), lam_o.numpy(), rtol=2e-5, atol=2e-6)
+    assert float(lam.cpu()[..., rows:].abs().max()) == 0.0 if lam.shape[-1] > rows else True
+    a, b = kp.cpu().view(torch.int16).int(), kp_o.view(torch.int16).int()
+    diff = (a - b).abs()
+    assert int(diff.max()) <= 1 and float((diff > 0).float().mean()) <= 5e-3
+
+
+def oracle_on_packed_operands(z, sm_scale, causal):
+    B, Hq, Hkv, Nq, Nk, D = z.shape
+    qc, qs = U.unpack_rows(z.q_codes, z.q_sf)
+    kc, ks = U.unpack_rows(z.k_codes, z.k_sf)
+    vc, vs = U.unpack_vt(z.vt_codes, z.vt_sf)
+    qd = torch.from_numpy(nvfp4.dequantize_nvfp4(qc, qs))
+    kd = torch.from_numpy(nvfp4.dequantize_nvfp4(kc, ks))
+    vtd = torch.from_numpy(nvfp4.dequantize_nvfp4(vc, vs))
+    ds = z.delta_s.float().cpu()
+    return sage3.attention_quantised(qd, kd, vtd, ds, Nq, z.nk_slots, sm_scale, causal, lamb=z.k_lambda.cpu())
+
+
+CASES = [
+    # B, Hq, Hkv, Nq, Nk, D, causal
+    (1, 2, 2, 128, 128, 128, False),
+    (1, 2, 2, 256, 240, 128, False),        # exactly two key tiles after packing
+    (1, 4, 4, 512, 512, 128, True),
+    (1, 8, 2, 640, 640, 128, True),         # GQA
+    (1, 2, 2, 200, 333, 128, False),        # ragged
+    (1, 2, 2, 333, 200, 128, True),         # causal with more queries than keys
+    (1, 2, 1, 200, 333, 128, True),
+    (1, 4, 2, 300, 300, 64, True),
+    (1, 4, 4, 512, 500, 64, False),
+    (1, 1, 1, 1, 1, 128, False),
+    (1, 1, 1, 17, 5, 64, True),
+]
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Nq,Nk,D,causal", CASES)
+def test_packed_kernel_matches_oracle_on_same_operands(B, Hq, Hkv, Nq, Nk, D, causal):
+    q, k, v = U.make_qkv(B, Hq, Hkv, Nq, Nk, D, seed=Nq + Nk + D + 1, device=DEV)
+    kp, vp, lam, _ = sa.pack_kv(k, v)
+    z = sa.quantize_qkv(q, kp, vp, per_block_mean=True, smooth_k=False)
+    z.k_lambda, z.nk_slots = lam, sage3.logical_to_packed_len(Nk)
+    out = sa.fp4_attention(z, is_causal=causal, check_status=True)
+    ref = oracle_on_packed_operands(z, D ** -0.5, causal)
+    cos, l1 = sage3.accuracy(out.float().cpu(), ref)
+    assert cos >= COS_MIN and l1 <= REL_L1_MAX, (cos, l1)
+
+
+@pytest.mark.parametrize("layout", ["HND", "NHD"])
+@pytest.mark.parametrize("causal", [False, True])
+def test_packed_operator_matches_emulation(layout, causal):
+    B, Hq, Hkv, N, D = 1, 4, 2, 700, 128
+    q, k, v = U.make_qkv(B, Hq, Hkv, N, N, D, seed=11, layout=layout, device=DEV)
+    out = sa.sageattn4_blackwell(q, k, v, tensor_layout=layout, is_causal=causal, check_status=True)
+    hnd = (lambda t: t.transpose(1, 2)) if layout == "NHD" else (lambda t: t)
+    emu = sage3.sageattn4_emulated(hnd(q).cpu().contiguous(), hnd(k).cpu().contiguous(), hnd(v).cpu().contiguous(),
+                                   is_causal=causal)
+    cos, l1 = sage3.accuracy(hnd(out).float().cpu(), emu.float())
+    assert cos >= COS_MIN and l1 <= REL_L1_MAX, (cos, l1)
+    sd = sage3.sdpa_fp32(hnd(q).cpu(), hnd(k).cpu(), hnd(v).cpu(), is_causal=causal)
+    cos_k, _ = sage3.accuracy(hnd(out).float().cpu(), sd)
+    cos_e, _ = sage3.accuracy(emu.float(), sd)
+    assert cos_k >= cos_e - 2e-3                                   # no worse than the emulation against fp32 SDPA
+
+
+def test_packed_mode_rejects_unsupported_variants():
+    q, k, v = U.make_qkv(1, 2, 2, 64, 64, 128, seed=1, device=DEV)
+    with pytest.raises(NotImplementedError):
+        sa.sageattn4_blackwell(q, k, v, per_block_mean=False)
+    with pytest.raises(AssertionError):
+        sa.sageattn4_blackwell(q, k, v, quant_block=8)
