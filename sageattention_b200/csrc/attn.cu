@@ -79,9 +79,10 @@ struct Smem {
   static constexpr int zero = b1 + kStages * 2 * 2048;    // second K chunk of every rank-1 operand; it must lie
                                                           // ABOVE them: the descriptor offset to it is unsigned
   static constexpr int dsraw = zero + 2048;               // [kStages][2][256] delta_s rows as loaded
-  static constexpr int lam = dsraw + kStages * 2 * 256;   // [kStages][128] f32: lambda of the key slots (K-packing mode),
-                                                          // loaded and released with the V stage
-  static constexpr int stats = lam + kStages * 512;       // [2][8 blocks][128 rows] float2 (exponent offset, scale)
+  static constexpr int lam = dsraw + kStages * 2 * 256;   // [2 * kStages][128] f32: lambda of the key slots (K-packing
+                                                          // mode), arrives with the K stage; twice as many slots as
+                                                          // stages because the softmax reads it after the stage is freed
+  static constexpr int stats = lam + 2 * kStages * 512;   // [2][8 blocks][128 rows] float2 (exponent offset, scale)
   static constexpr int bars = stats + 2 * 8 * 128 * 8;
   static constexpr int total = bars + 512;
 };
@@ -169,16 +170,18 @@ __device__ __forceinline__ float max16(const uint32_t* r) {
 // per-block scales (P blockmax / 6) as E4M3 bytes for the PV MMA (`sfp`) and, unrounded, in `st`.
 // K-packing mode (fwd_mainloop.cu:796-845, 878-881): a block of 16 keys is one group - slot 0 holds the
 // score of the group mean, which every other score of the group gets added lambda times; the slot itself
-// carries no token and is masked out.
-__device__ __forceinline__ void apply_lambda(uint32_t (&r)[16], const float* lam16) {
+// carries no token and is masked out.  Done once, in pass 1, which writes the corrected scores back to
+// tensor memory for pass 2.
+__device__ __forceinline__ void apply_lambda(uint32_t (&r)[16], const float4 (&lq)[4]) {
   const float s0 = __uint_as_float(r[0]);
+  const float2 s02 = make_float2(s0, s0);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const float4 l4 = *reinterpret_cast<const float4*>(lam16 + 4 * i);
-    if (i > 0) r[4 * i] = __float_as_uint(fmaf(l4.x, s0, __uint_as_float(r[4 * i])));
-    r[4 * i + 1] = __float_as_uint(fmaf(l4.y, s0, __uint_as_float(r[4 * i + 1])));
-    r[4 * i + 2] = __float_as_uint(fmaf(l4.z, s0, __uint_as_float(r[4 * i + 2])));
-    r[4 * i + 3] = __float_as_uint(fmaf(l4.w, s0, __uint_as_float(r[4 * i + 3])));
+    const float4 l4 = lq[i];
+    const float2 a = ffma2(make_float2(l4.x, l4.y), s02, make_float2(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1])));
+    const float2 b = ffma2(make_float2(l4.z, l4.w), s02, make_float2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])));
+    r[4 * i] = __float_as_uint(a.x); r[4 * i + 1] = __float_as_uint(a.y);
+    r[4 * i + 2] = __float_as_uint(b.x); r[4 * i + 3] = __float_as_uint(b.y);
   }
   r[0] = 0xff800000u;
 }
@@ -188,26 +191,46 @@ __device__ __forceinline__ float softmax_pass1_impl(const uint32_t tm_S, const f
                                                     uint2& sfp, const int n0, const int key_lim, const float* lam_s) {
   uint32_t ra[16], rb[16];
   float bm[8];
+  float4 la[4], lb[4];                                      // lambdas of the block in ra / rb, fetched one block ahead
   tmem_ld16(tm_S, ra);
+  if (kPacked) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) la[i] = reinterpret_cast<const float4*>(lam_s)[i];
+  }
 #pragma unroll
   for (int blk = 0; blk < 8; blk += 2) {
+    if (kPacked) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) lb[i] = reinterpret_cast<const float4*>(lam_s + (blk + 1) * 16)[i];
+    }
     tmem_wait_ld();
     tmem_ld16(tm_S + (blk + 1) * 16, rb);
-    if (kPacked) apply_lambda(ra, lam_s + blk * 16);
+    if (kPacked) {
+      apply_lambda(ra, la);
+      tmem_st16(tm_S + blk * 16, ra);
+    }
     if (kMask) {
 #pragma unroll
       for (int i = 0; i < 16; ++i) ra[i] = (n0 + blk * 16 + i > key_lim) ? 0xff800000u : ra[i];
     }
     bm[blk] = max16(ra);
+    if (kPacked && blk + 2 < 8) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) la[i] = reinterpret_cast<const float4*>(lam_s + (blk + 2) * 16)[i];
+    }
     tmem_wait_ld();
     if (blk + 2 < 8) tmem_ld16(tm_S + (blk + 2) * 16, ra);
-    if (kPacked) apply_lambda(rb, lam_s + (blk + 1) * 16);
+    if (kPacked) {
+      apply_lambda(rb, lb);
+      tmem_st16(tm_S + (blk + 1) * 16, rb);
+    }
     if (kMask) {
 #pragma unroll
       for (int i = 0; i < 16; ++i) rb[i] = (n0 + (blk + 1) * 16 + i > key_lim) ? 0xff800000u : rb[i];
     }
     bm[blk + 1] = max16(rb);
   }
+  if (kPacked) tmem_wait_st();
   const float m_new = fmax3(fmax3(bm[0], bm[1], bm[2]), fmax3(bm[3], bm[4], bm[5]), fmax3(bm[6], bm[7], m));
   const float m_fin = (m_new == -INFINITY) ? 0.f : m_new;
   const float alpha = ex2_approx((m - m_fin) * c);          // 0 on the first tile
@@ -244,7 +267,6 @@ __device__ __forceinline__ void softmax_pass2_impl(const uint32_t tm_S, const fl
     tmem_wait_ld();
     if (blk < 7) tmem_ld16(tm_S + (blk + 1) * 16, rn);
     const float2 ns_next = st[((blk + 1) & 7) * 128];
-    if (kPacked) apply_lambda(r, lam_s + blk * 16);
     if (kMask) {
 #pragma unroll
       for (int i = 0; i < 16; ++i) r[i] = (n0 + blk * 16 + i > key_lim) ? 0xff800000u : r[i];
@@ -444,7 +466,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
             if (!(ok = wait_bar<false>(bars + Bars::k_empty + 8 * s, ph, abort_s, P.status, 10))) break;
             const uint32_t kb = bars + Bars::k_full + 8 * s;
             const int nds = has_ds ? (int)(j < wk.n_t[0]) + (int)(j < wk.n_t[1]) : 0;
-            mbar_arrive_expect_tx(kb, L::kKBytes + L::kSfRow + 256 * nds);
+            mbar_arrive_expect_tx(kb, L::kKBytes + L::kSfRow + 256 * nds + (kPacked ? 512 : 0));
+            if (kPacked) bulk_load(sbase + L::lam + (g % (2 * kStages)) * 512, P.lam + (kvhead + j) * kBlockN, 512, kb);
             tma_load_2d(sbase + L::k + s * L::kKBytes, &tm_k, 0, (int)((kvhead + j) * kBlockN), kb);
             bulk_load(sbase + L::sfk + s * 1024, P.k_sf + (kvhead + j) * L::kSfRow, L::kSfRow, kb);
             if (has_ds) {
@@ -456,10 +479,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
             ++gk;
             if (!(ok = wait_bar<false>(bars + Bars::v_empty + 8 * s, ph, abort_s, P.status, 11))) break;
             const uint32_t vb = bars + Bars::v_full + 8 * s;
-            mbar_arrive_expect_tx(vb, L::kVBytes + L::kSfV + (kPacked ? 512 : 0));
+            mbar_arrive_expect_tx(vb, L::kVBytes + L::kSfV);
             tma_load_2d(sbase + L::v + s * L::kVBytes, &tm_v, 0, (int)((kvhead + j) * D), vb);
             bulk_load(sbase + L::sfv + s * 1024, P.vt_sf + (kvhead + j) * L::kSfV, L::kSfV, vb);
-            if (kPacked) bulk_load(sbase + L::lam + s * 512, P.lam + (kvhead + j) * kBlockN, 512, vb);
           }
         }
         if (*abort_s) {
@@ -664,11 +686,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           const bool need_mask = (n0 + kBlockN - 1 >= P.Nk) || (kCausal && n0 + kBlockN - 1 > first_row_lim);
           const float* lam_s = nullptr;
           if (kPacked) {
-            // lambda of this key tile travels with its V stage (released only after both tiles' P.V MMAs, i.e.
-            // after every reader here is done); the stage has normally landed long before
+            // lambda of this key tile arrived with its K stage, i.e. before the Q.K^T MMA whose completion is
+            // awaited next.  Its slot is rewritten 2*kStages key tiles later, which the producer can only do
+            // after the Q.K^T of tile g+kStages is complete - issued after both warpgroups finished tile g.
             const uint32_t g = g_first + (uint32_t)it;
-            if (!(ok = wait_bar<false>(bars + Bars::v_full + 8 * (g % kStages), (g / kStages) & 1, abort_s, P.status, 33))) break;
-            lam_s = reinterpret_cast<const float*>(smem + L::lam) + (g % kStages) * 128;
+            lam_s = reinterpret_cast<const float*>(smem + L::lam) + (g % (2 * kStages)) * 128;
           }
           if (!(ok = wait_bar<false>(bar_s, sc & 1, abort_s, P.status, 30))) break;
           tc_fence_after();
