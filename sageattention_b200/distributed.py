@@ -15,6 +15,12 @@ head count, ``:31-36``).  Two schemes are provided:
   Heads are processed in chunks so that the exchange of chunk ``i+1`` overlaps the attention of
   chunk ``i``.  Every exchanged tile lands in local HBM first; the kernels only ever read local
   memory.
+* **ring (context-parallel) attention** for sequences too long for the all-to-all scheme (or head
+  counts that the world size does not divide): K/V shards travel round a ring of point-to-point
+  copies while every rank attends its own queries to the shard it currently holds; the partial
+  outputs are merged with their log-sum-exp (:func:`ring_attention`, :func:`merge_partial`).  Each
+  step quantises and smooths its K shard on its own, which is exact for the merge because the
+  operator's LSE output already carries the K-mean correction.
 """
 from __future__ import annotations
 
@@ -133,6 +139,60 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group=N
         return outs[0]
     # chunk c carried global heads [c*hc, (c+1)*hc): rank p's part of it sits at [p*hc/P, (p+1)*hc/P)
     return torch.cat(outs, dim=2)
+
+
+def merge_partial(out_a: torch.Tensor, lse_a: torch.Tensor, out_b: torch.Tensor, lse_b: torch.Tensor):
+    """Merge two attention results over disjoint key sets.  ``out`` [B,N,H,D] (NHD), ``lse`` [B,H,N]
+    natural-log sum of exp(scores); rows that saw no key carry ``lse = -inf`` (or ``+inf``, which the
+    kernel writes for tiles without keys) and weight 0."""
+    la = torch.where(torch.isfinite(lse_a), lse_a, torch.full_like(lse_a, -float("inf")))
+    lb = torch.where(torch.isfinite(lse_b), lse_b, torch.full_like(lse_b, -float("inf")))
+    lse = torch.logaddexp(la, lb)
+    safe = torch.where(torch.isfinite(lse), lse, torch.zeros_like(lse))
+    wa = torch.exp(la - safe).transpose(1, 2).unsqueeze(-1)                 # [B,N,H,1]
+    wb = torch.exp(lb - safe).transpose(1, 2).unsqueeze(-1)
+    out = out_a.float() * wa + out_b.float() * wb
+    return out, lse
+
+
+def ring_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group=None, is_causal: bool = False,
+                   attn_fn: Optional[Callable] = None, **kwargs) -> torch.Tensor:
+    """Context-parallel attention.  q, k, v: this rank's sequence shard ``[B, N/P, H(kv), D]`` ("NHD";
+    shard r holds tokens ``r*N/P ... (r+1)*N/P - 1``; GQA allowed).  Returns the output shard.
+
+    ``attn_fn(q, k, v, tensor_layout="NHD", is_causal=..., return_lse=True)`` must return
+    ``(out, lse)`` like :func:`sageattention_b200.sageattn`.  Step ``s`` attends to the shard of rank
+    ``r - s``; the shard for step ``s + 1`` is in flight (one send, one receive per rank over
+    NVLink / NVSwitch, into local HBM) while step ``s`` computes.  Causal: the own shard is attended
+    with the causal mask, shards of lower ranks in full, shards of higher ranks are skipped (they are
+    still forwarded)."""
+    if attn_fn is None:
+        from .api import sageattn as attn_fn
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    send_to = dist.get_global_rank(group, (rank + 1) % world) if group is not None else (rank + 1) % world
+    recv_from = dist.get_global_rank(group, (rank - 1) % world) if group is not None else (rank - 1) % world
+    kv = torch.stack([k, v]).contiguous()                       # one message per step
+    out, lse = None, None
+    for s in range(world):
+        nxt, reqs = None, []
+        if s + 1 < world:
+            nxt = torch.empty_like(kv)
+            ops = [dist.P2POp(dist.isend, kv, send_to, group), dist.P2POp(dist.irecv, nxt, recv_from, group)]
+            reqs = dist.batch_isend_irecv(ops)
+        src = (rank - s) % world                                 # whose shard kv holds now
+        if not (is_causal and src > rank):
+            o, l = attn_fn(q, kv[0], kv[1], tensor_layout="NHD", is_causal=bool(is_causal and src == rank),
+                           return_lse=True, **kwargs)
+            if out is None:
+                out, lse = o.float(), l
+            else:
+                out, lse = merge_partial(out, lse, o, l)
+        for r in reqs:
+            r.wait()
+        if nxt is not None:
+            kv = nxt
+    return out.to(q.dtype)
 
 
 # ----------------------------------------------------------------------------------------------------

@@ -178,3 +178,14 @@ def test_host_tensor_entry_point_matches_device_operator():
         got = sa.sageattn_from_host(q.pin_memory(), k.pin_memory(), v.pin_memory(), head_chunks=chunks, is_causal=True)
         torch.cuda.synchronize()
         assert torch.equal(got, want), chunks
+
+
+def test_custom_op_runs_and_matches_direct_call():
+    from sageattention_b200 import compile_ops
+    q, k, v = U.make_qkv(1, 4, 2, 300, 300, 128, seed=5, device=DEV)
+    for packing in (False, True):
+        direct = (sa.sageattn4_blackwell if packing else sa.sageattn3_blackwell)(q, k, v, is_causal=True)
+        via_op = compile_ops.sageattn_compilable(q, k, v, is_causal=True, k_packing=packing)
+        assert torch.equal(direct, via_op)
+    torch.library.opcheck(compile_ops.fp4_attention_op, (q, k, v, "HND", False, 0.0, True, False),
+                          test_utils=("test_schema", "test_faketensor"))

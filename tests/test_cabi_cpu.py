@@ -78,3 +78,17 @@ def test_front_end_refuses_cpu_tensors():
     q = torch.zeros(1, 1, 128, 128, dtype=torch.bfloat16)
     with pytest.raises(ValueError):
         sa.sageattn(q, q, q)
+
+
+def test_custom_op_fake_needs_no_gpu():
+    """The torch.library registration (the reference does this for its INT8 kernels,
+    sageattention/sm89_compile.py:5-101): shape propagation through the fake implementation."""
+    import torch
+    from sageattention_b200 import compile_ops
+    q = torch.empty((2, 8, 300, 128), dtype=torch.bfloat16, device="meta")
+    k = torch.empty((2, 2, 500, 128), dtype=torch.bfloat16, device="meta")
+    out = compile_ops.sageattn_compilable(q, k, k, is_causal=True)
+    assert out.shape == q.shape and out.dtype == torch.bfloat16 and out.device.type == "meta"
+    out = compile_ops.sageattn_compilable(q.transpose(1, 2), k.transpose(1, 2), k.transpose(1, 2), tensor_layout="NHD",
+                                          k_packing=True)
+    assert out.shape == (2, 300, 8, 128)

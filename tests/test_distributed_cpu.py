@@ -48,6 +48,57 @@ def _worker(rank, world, port, chunks, ret):
         dist.destroy_process_group()
 
 
+def _sdpa_lse_fn(q, k, v, tensor_layout="NHD", is_causal=False, return_lse=True, **kw):
+    """fp32 attention with log-sum-exp, NHD, GQA, top-left = bottom-right causal (equal lengths)."""
+    qh, kh, vh = (t.transpose(1, 2).float() for t in (q, k, v))
+    g = qh.shape[1] // kh.shape[1]
+    kh, vh = kh.repeat_interleave(g, dim=1), vh.repeat_interleave(g, dim=1)
+    s = torch.matmul(qh, kh.transpose(-1, -2)) * qh.shape[-1] ** -0.5
+    if is_causal:
+        n = s.shape[-1]
+        s = s.masked_fill(torch.ones(n, n, dtype=torch.bool).triu(1), float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    o = torch.matmul(torch.softmax(s, dim=-1), vh)
+    return o.transpose(1, 2).contiguous(), lse
+
+
+def _ring_worker(rank, world, port, causal, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(1)
+        B, N, Hq, Hkv, D = 2, 96, 4, 2, 16
+        q = torch.randn(B, N, Hq, D, generator=g)
+        k, v = (torch.randn(B, N, Hkv, D, generator=g) for _ in range(2))
+        n = N // world
+        sl = slice(rank * n, (rank + 1) * n)
+        out = sd.ring_attention(q[:, sl].contiguous(), k[:, sl].contiguous(), v[:, sl].contiguous(),
+                                is_causal=causal, attn_fn=_sdpa_lse_fn)
+        want, _ = _sdpa_lse_fn(q, k, v, is_causal=causal)
+        ret[rank] = bool(torch.allclose(out, want[:, sl], atol=1e-5))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,causal", [(2, False), (2, True), (3, True)])
+def test_ring_attention_matches_single_process(world, causal):
+    port = _free_port()
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_ring_worker, args=(world, port, causal, ret), nprocs=world, join=True)
+        assert dict(ret) == {r: True for r in range(world)}
+
+
+def test_merge_partial_ignores_rows_without_keys():
+    o1, o2 = torch.randn(1, 4, 2, 8), torch.randn(1, 4, 2, 8)
+    l1 = torch.randn(1, 2, 4)
+    l2 = torch.full((1, 2, 4), float("inf"))                   # what the kernel writes for tiles without keys
+    out, lse = sd.merge_partial(o1, l1, o2, l2)
+    assert torch.allclose(out, o1) and torch.allclose(lse, l1)
+    out, lse = sd.merge_partial(o1, torch.full_like(l1, -float("inf")), o2, l2)
+    assert torch.equal(out, torch.zeros_like(out))
+
+
 @pytest.mark.parametrize("chunks", [1, 2])
 def test_ulysses_and_head_sharding_match_single_process(chunks):
     world = 2
