@@ -29,7 +29,8 @@
 //   warp 10     turns each delta_s row (128 bf16) into the B operand of a rank-1 bf16 MMA
 //               (ones x delta_s) that initialises the score accumulator, so the softmax warps never
 //               touch delta_s
-//   warp 11     PV issuer (one lane): scale-factor copies and P.V MMAs for both tiles
+//   warp 11     PV issuer (one lane): scale-factor copies and P.V MMAs for both tiles; the MMA over keys 0-63
+//               of a tile is issued as soon as the softmax has written that half of P^ (its own barrier)
 //
 // Tensor memory (512 columns): S0 [0,128) S1 [128,256) PV product [256,256+D) (shared by both
 // tiles, drained into registers right after each PV MMA) and 48 columns of scale factors.
@@ -100,7 +101,8 @@ struct Bars {            // byte offsets inside the barrier block
   static constexpr int o_full = p_full + 16;              // [2]
   static constexpr int o_free = o_full + 16;
   static constexpr int drain = o_free + 8;                // [2] the issuers' last commit when giving up
-  static constexpr int tmem_slot = drain + 16;             // u32 written by tcgen05.alloc
+  static constexpr int p_half = drain + 16;               // [2] first 64 keys of P^ (and their scales) written
+  static constexpr int tmem_slot = p_half + 16;             // u32 written by tcgen05.alloc
   static constexpr int abort_flag = tmem_slot + 8;
   static constexpr int run_flag = abort_flag + 4;
 };
@@ -253,7 +255,7 @@ __device__ __forceinline__ float softmax_pass1_impl(const uint32_t tm_S, const f
 template <bool kMask, bool kPacked>
 __device__ __forceinline__ void softmax_pass2_impl(const uint32_t tm_S, const float c, const float alpha, float& l,
                                                    const float2* st, uint8_t* p_row, const int swz, const int n0,
-                                                   const int key_lim, const float* lam_s) {
+                                                   const int key_lim, const float* lam_s, const uint32_t bar_half) {
   uint32_t ra[16], rb[16];
   const float2 c2 = make_float2(c, c);
   float lsum = 0.f;
@@ -284,6 +286,11 @@ __device__ __forceinline__ void softmax_pass2_impl(const uint32_t tm_S, const fl
     code[(blk & 1) * 2 + 0] = f32x8_to_e2m1x8(e[0].x, e[0].y, e[1].x, e[1].y, e[2].x, e[2].y, e[3].x, e[3].y);
     code[(blk & 1) * 2 + 1] = f32x8_to_e2m1x8(e[4].x, e[4].y, e[5].x, e[5].y, e[6].x, e[6].y, e[7].x, e[7].y);
     if (blk & 1) *reinterpret_cast<uint4*>(p_row + (((blk >> 1) ^ swz) << 4)) = make_uint4(code[0], code[1], code[2], code[3]);
+    if (blk == 3) {
+      // keys 0-63 of P^ and their scales are in shared memory: the first half of the P.V MMA can be issued
+      fence_proxy_async_smem();
+      mbar_arrive(bar_half);
+    }
     ns = ns_next;
   }
   l = fmaf(l, alpha, lsum);
@@ -299,8 +306,8 @@ __device__ __noinline__ float softmax_pass1_masked(const uint32_t tm_S, const fl
 template <bool kPacked>
 __device__ __noinline__ void softmax_pass2_masked(const uint32_t tm_S, const float c, const float alpha, float& l,
                                                   const float2* st, uint8_t* p_row, const int swz, const int n0,
-                                                  const int key_lim, const float* lam_s) {
-  softmax_pass2_impl<true, kPacked>(tm_S, c, alpha, l, st, p_row, swz, n0, key_lim, lam_s);
+                                                  const int key_lim, const float* lam_s, const uint32_t bar_half) {
+  softmax_pass2_impl<true, kPacked>(tm_S, c, alpha, l, st, p_row, swz, n0, key_lim, lam_s, bar_half);
 }
 
 // K-packing mode: 15 tokens occupy 16 key slots (fwd_mainloop.cu:273-303).  Last slot that token `tok` or an
@@ -388,6 +395,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       mbar_init(bars + Bars::q_empty + 8 * t, 1);          // tcgen05.commit after the last QK that reads the tile
       mbar_init(bars + Bars::s_full + 8 * t, 1);
       mbar_init(bars + Bars::p_full + 8 * t, 128);
+      mbar_init(bars + Bars::p_half + 8 * t, 128);
       mbar_init(bars + Bars::o_full + 8 * t, 1);
     }
     for (int s = 0; s < kStages; ++s) {
@@ -611,15 +619,18 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
             for (int t = 0; t < 2; ++t) {
               const bool act = t == 0 ? (j < wk.n_t[0]) : act1;
               if (!(ok && act)) continue;
-              if (!(ok = wait_bar<kIssuerHint>(bars + Bars::p_full + 8 * t, pv_cnt[t] & 1, abort_s, P.status, 26))) break;
+              // first half (keys 0-63) as soon as the softmax has written it, while it still works on the rest
+              if (!(ok = wait_bar<kIssuerHint>(bars + Bars::p_half + 8 * t, pv_cnt[t] & 1, abort_s, P.status, 27))) break;
               if (pv_total > 0 && !(ok = wait_bar<kIssuerHint>(bars + Bars::o_free, (pv_total - 1) & 1, abort_s, P.status, 22))) break;
               tc_fence_after();
-#pragma unroll
-              for (int kb = 0; kb < 2; ++kb) tc_cp_sf(tm_sfp + 8 * t + 4 * kb, sfp_lo + t * 64 + kb * 32, HI_SF);
-#pragma unroll
-              for (int kb = 0; kb < 2; ++kb)
-                tc_mma_nvf4(tm_O, p_lo + t * (L::kPBytes >> 4) + kb * 2, HI_PV, v_lo + s * (L::kVBytes >> 4) + kb * 2, HI_PV,
-                            idesc_pv, tm_sfp + 8 * t + 4 * kb, tm_sfv + 4 * kb, kb > 0);
+              tc_cp_sf(tm_sfp + 8 * t, sfp_lo + t * 64, HI_SF);
+              tc_mma_nvf4(tm_O, p_lo + t * (L::kPBytes >> 4), HI_PV, v_lo + s * (L::kVBytes >> 4), HI_PV, idesc_pv,
+                          tm_sfp + 8 * t, tm_sfv, 0);
+              if (!(ok = wait_bar<kIssuerHint>(bars + Bars::p_full + 8 * t, pv_cnt[t] & 1, abort_s, P.status, 26))) break;
+              tc_fence_after();
+              tc_cp_sf(tm_sfp + 8 * t + 4, sfp_lo + t * 64 + 32, HI_SF);
+              tc_mma_nvf4(tm_O, p_lo + t * (L::kPBytes >> 4) + 2, HI_PV, v_lo + s * (L::kVBytes >> 4) + 2, HI_PV, idesc_pv,
+                          tm_sfp + 8 * t + 4, tm_sfv + 4, 1);
               tc_commit(bars + Bars::o_full + 8 * t);
               ++pv_cnt[t];
               ++pv_total;
@@ -645,7 +656,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       float2* st = reinterpret_cast<float2*>(smem + L::stats) + t * 8 * 128 + row;
       uint32_t* sfp_row = reinterpret_cast<uint32_t*>(smem + L::sfp + t * 1024 + sf_atom_offset(row, 0));
       const uint32_t bar_s = bars + Bars::s_full + 8 * t, bar_p = bars + Bars::p_full + 8 * t;
-      const uint32_t bar_o = bars + Bars::o_full + 8 * t;
+      const uint32_t bar_o = bars + Bars::o_full + 8 * t, bar_h = bars + Bars::p_half + 8 * t;
       uint32_t sc = 0;                                           // key tiles processed so far by this warpgroup
       uint32_t g0 = 0;                                           // K/V stages the CTA used before this work item
       bool ok = true;
@@ -699,8 +710,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
                                         : softmax_pass1_impl<false, kPacked>(tm_S, c, m, st, sfp, 0, 0, lam_s);
           sfp_row[0] = sfp.x;
           sfp_row[128] = sfp.y;
-          if (need_mask) softmax_pass2_masked<kPacked>(tm_S, c, alpha, l, st, p_row, swz, n0, key_lim, lam_s);
-          else softmax_pass2_impl<false, kPacked>(tm_S, c, alpha, l, st, p_row, swz, 0, 0, lam_s);
+          if (need_mask) softmax_pass2_masked<kPacked>(tm_S, c, alpha, l, st, p_row, swz, n0, key_lim, lam_s, bar_h);
+          else softmax_pass2_impl<false, kPacked>(tm_S, c, alpha, l, st, p_row, swz, 0, 0, lam_s, bar_h);
           // S consumed and P^ written: hand both to the MMA issuers
           tc_fence_before();
           fence_proxy_async_smem();
