@@ -355,7 +355,8 @@ def sageattn_from_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: O
                        **kwargs) -> torch.Tensor:
     """Attention on HOST tensors (HND ``[B,H,N,D]`` bf16, ideally pinned): the heads are processed in
     ``head_chunks`` groups of kv heads, and the host-to-device copy of group ``i+1`` and the
-    device-to-host copy of group ``i-1`` run on their own streams while group ``i`` is computed, so the
+    device-to-host copy of group ``i-1`` run on their own streams while group ``i`` is computed (groups
+    alternate between two compute streams so that their kernels overlap at the seams), so the
     PCIe transfers hide behind the kernels (or the other way round).  Returns the output as a host tensor
     (``out`` if given, else a new pinned tensor).  The work is ordered after the caller's current stream
     and the current stream waits for the last copy, so CUDA events recorded around the call time all of it;
@@ -373,12 +374,13 @@ def sageattn_from_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: O
     chunks = max(1, min(head_chunks, Hkv))
     bounds = [(Hkv * c) // chunks for c in range(chunks + 1)]
     if dev not in _host_streams:
-        _host_streams[dev] = (torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev))
-    s_in, s_run, s_out = _host_streams[dev]
+        _host_streams[dev] = tuple(torch.cuda.Stream(dev) for _ in range(4))
+    s_in, s_run_a, s_run_b, s_out = _host_streams[dev]
     cur = torch.cuda.current_stream(dev)
     start = torch.cuda.Event()
     start.record(cur)
-    s_in.wait_event(start)
+    for st in (s_in, s_run_a, s_run_b, s_out):
+        st.wait_event(start)
     keep = []
     for c in range(chunks):
         h0, h1 = bounds[c], bounds[c + 1]
@@ -390,6 +392,9 @@ def sageattn_from_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: O
             vd = v[:, h0:h1].to(dev, non_blocking=True)
             ev_in = torch.cuda.Event()
             ev_in.record(s_in)
+        # groups alternate between two compute streams: the attention kernel is persistent (one CTA per SM), so
+        # the kernels of the next group fill the SMs that the last, partly filled round of this group leaves idle
+        s_run = s_run_a if c % 2 == 0 else s_run_b
         with torch.cuda.stream(s_run):
             s_run.wait_event(ev_in)
             od = sageattn3_blackwell(qd, kd, vd, tensor_layout="HND", is_causal=is_causal, sm_scale=sm_scale, **kwargs)
@@ -402,6 +407,10 @@ def sageattn_from_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: O
     done = torch.cuda.Event()
     done.record(s_out)
     cur.wait_event(done)
+    for st in (s_run_a, s_run_b):                 # nothing of this call may outlive the caller's next operation
+        ev = torch.cuda.Event()
+        ev.record(st)
+        cur.wait_event(ev)
     # the device buffers were allocated on side streams: tell the allocator the current stream orders their reuse
     for tensors in keep:
         for t in tensors:
