@@ -323,7 +323,8 @@ def sageattn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlen
                     sm_scale: Optional[float] = None, smooth_k: bool = True, **kwargs) -> torch.Tensor:
     """Variable-length batch (``sageattention/core.py:334-448``): q ``[sum(len_q), Hq, D]``, k/v
     ``[sum(len_k), Hkv, D]``, ``cu_seqlens_*`` the int32 prefix sums (length batch + 1).  Each sequence
-    is smoothed, quantised and attended on its own (K means never mix sequences)."""
+    is smoothed, quantised and attended on its own (K means never mix sequences); neighbouring sequences of
+    equal length share one batched launch."""
     if q.dim() != 3 or k.dim() != 3 or v.dim() != 3:
         raise ValueError("varlen tensors must be [tokens, heads, head_dim]")
     cq = cu_seqlens_q.tolist()
@@ -331,23 +332,57 @@ def sageattn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlen
     if len(cq) != len(ck) or cq[0] != 0 or ck[0] != 0:
         raise ValueError("cu_seqlens_q and cu_seqlens_k must both start at 0 and have batch + 1 entries")
     out = torch.empty_like(q)
-    for i in range(len(cq) - 1):
+    nseq = len(cq) - 1
+    # runs of neighbouring sequences with equal lengths are one batched call (a view, no copy); different
+    # runs go to a small pool of streams so that the kernels of short sequences, which cannot fill the GPU
+    # on their own, overlap
+    runs = []
+    i = 0
+    while i < nseq:
         lq, lk = cq[i + 1] - cq[i], ck[i + 1] - ck[i]
         if lq > max_seqlen_q or lk > max_seqlen_k:
             raise ValueError("sequence longer than max_seqlen")
-        if lq == 0:
-            continue
-        if lk == 0:
-            out[cq[i]:cq[i + 1]].zero_()
-            continue
-        oi = sageattn3_blackwell(q[cq[i]:cq[i + 1]].unsqueeze(0), k[ck[i]:ck[i + 1]].unsqueeze(0),
-                                 v[ck[i]:ck[i + 1]].unsqueeze(0), tensor_layout="NHD", is_causal=is_causal,
-                                 sm_scale=sm_scale, smooth_k=smooth_k, **kwargs)
-        out[cq[i]:cq[i + 1]] = oi[0]
+        j = i + 1
+        while j < nseq and cq[j + 1] - cq[j] == lq and ck[j + 1] - ck[j] == lk:
+            j += 1
+        runs.append((i, j, lq, lk))
+        i = j
+    dev = q.device
+    work = [r for r in runs if r[2] > 0 and r[3] > 0]
+    for (a, b, lq, lk) in runs:
+        if lq > 0 and lk == 0:
+            out[cq[a]:cq[b]].zero_()
+    use_pool = len(work) > 1
+    if use_pool:
+        if dev not in _varlen_streams:
+            _varlen_streams[dev] = tuple(torch.cuda.Stream(dev) for _ in range(4))
+        cur = torch.cuda.current_stream(dev)
+        fork = torch.cuda.Event()
+        fork.record(cur)
+    for n, (a, b, lq, lk) in enumerate(work):
+        H, Hk, D = q.shape[1], k.shape[1], q.shape[2]
+        qi = q[cq[a]:cq[b]].view(b - a, lq, H, D)
+        ki = k[ck[a]:ck[b]].view(b - a, lk, Hk, D)
+        vi = v[ck[a]:ck[b]].view(b - a, lk, Hk, D)
+        st = _varlen_streams[dev][n % 4] if use_pool else torch.cuda.current_stream(dev)
+        with torch.cuda.stream(st):
+            if use_pool:
+                st.wait_event(fork)
+            oi = sageattn3_blackwell(qi, ki, vi, tensor_layout="NHD", is_causal=is_causal, sm_scale=sm_scale,
+                                     smooth_k=smooth_k, **kwargs)
+            out[cq[a]:cq[b]] = oi.view(-1, H, D)
+            if use_pool:
+                oi.record_stream(st)
+    if use_pool:
+        for st in _varlen_streams[dev]:
+            ev = torch.cuda.Event()
+            ev.record(st)
+            cur.wait_event(ev)
     return out
 
 
 _host_streams = {}
+_varlen_streams = {}
 
 
 def sageattn_from_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[torch.Tensor] = None,
@@ -371,8 +406,23 @@ def sageattn_from_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: O
     g = Hq // Hkv
     if out is None:
         out = torch.empty_like(q).pin_memory()
-    chunks = max(1, min(head_chunks, Hkv))
-    bounds = [(Hkv * c) // chunks for c in range(chunks + 1)]
+    # group sizes: about Hkv / head_chunks heads, but ramping up from one head at the start and down to one at
+    # the end, so that the first kernel starts after a small copy and little is left to copy out after the last
+    base = max(1, Hkv // max(1, min(head_chunks, Hkv)))
+    ramp = [n for n in (1, 2, 4) if n < base]
+    sizes = list(ramp)
+    left = Hkv - sum(ramp)
+    tail = [n for n in reversed(ramp) if n <= left - base]      # keep at least one full group in the middle
+    left -= sum(tail)
+    while left > 0:
+        sizes.append(min(base, left))
+        left -= sizes[-1]
+    sizes += tail
+    bounds = [0]
+    for n in sizes:
+        bounds.append(bounds[-1] + n)
+    assert bounds[-1] == Hkv
+    chunks = len(sizes)
     if dev not in _host_streams:
         _host_streams[dev] = tuple(torch.cuda.Stream(dev) for _ in range(4))
     s_in, s_run_a, s_run_b, s_out = _host_streams[dev]

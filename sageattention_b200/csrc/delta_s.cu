@@ -17,7 +17,7 @@
 namespace sage3 {
 
 template <int D>
-__global__ void __launch_bounds__(256) delta_s_kernel(
+__global__ void __launch_bounds__(256, 3) delta_s_kernel(
     const __nv_bfloat16* __restrict__ qm, const __nv_bfloat16* __restrict__ k, int64_t k_sb, int64_t k_sh,
     int64_t k_sn, const __nv_bfloat16* __restrict__ km, __nv_bfloat16* __restrict__ ds, int Hq, int Hkv, int Tq,
     int Nk, int Nk_pad) {
@@ -27,6 +27,26 @@ __global__ void __launch_bounds__(256) delta_s_kernel(
   __nv_bfloat16* cs = ks + 128 * PITCH;                                        // [8 warps][16][136]
   const int tile = blockIdx.x, bh = blockIdx.y, b = bh / Hkv, hkv = bh % Hkv, G = Hq / Hkv;
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31, g = lane >> 2, tg = lane & 3;
+
+  // A fragments (rows m0+g and m0+g+8 of the stacked block means of this GQA group) come from global memory /
+  // L2; the first set is requested before the K tile is built and the next one while the current one is
+  // multiplied, so their latency is not on the critical path
+  const int M = G * Tq;
+  auto load_a = [&](uint32_t (&a)[D / 16][4], const int m0) {
+    const int r0 = m0 + g, r1 = m0 + g + 8;
+    const uint32_t* p0 = nullptr; const uint32_t* p1 = nullptr;
+    if (r0 < M) p0 = reinterpret_cast<const uint32_t*>(qm + (((int64_t)b * Hq + hkv * G + r0 / Tq) * Tq + r0 % Tq) * D);
+    if (r1 < M) p1 = reinterpret_cast<const uint32_t*>(qm + (((int64_t)b * Hq + hkv * G + r1 / Tq) * Tq + r1 % Tq) * D);
+#pragma unroll
+    for (int s = 0; s < D / 16; ++s) {
+      a[s][0] = p0 ? __ldg(p0 + s * 8 + tg) : 0u;
+      a[s][1] = p1 ? __ldg(p1 + s * 8 + tg) : 0u;
+      a[s][2] = p0 ? __ldg(p0 + s * 8 + 4 + tg) : 0u;
+      a[s][3] = p1 ? __ldg(p1 + s * 8 + 4 + tg) : 0u;
+    }
+  };
+  uint32_t a_next[D / 16][4];
+  load_a(a_next, warp * 16);
 
   {  // smoothed K tile -> shared
     constexpr int CH = D / 8, RPP = 256 / CH;
@@ -38,38 +58,36 @@ __global__ void __launch_bounds__(256) delta_s_kernel(
       mean[4] = bf16_lo(m.z); mean[5] = bf16_hi(m.z); mean[6] = bf16_lo(m.w); mean[7] = bf16_hi(m.w);
     }
     const __nv_bfloat16* src = k + b * k_sb + hkv * k_sh + c * 8;
+    uint4 w[128 / RPP];
+#pragma unroll
+    for (int p = 0; p < 128 / RPP; ++p) {                  // all loads in flight before the first use
+      const int n = tile * 128 + p * RPP + rl;
+      w[p] = make_uint4(0, 0, 0, 0);
+      if (n < Nk) w[p] = *reinterpret_cast<const uint4*>(src + (int64_t)n * k_sn);
+    }
 #pragma unroll
     for (int p = 0; p < 128 / RPP; ++p) {
       const int r = p * RPP + rl, n = tile * 128 + r;
-      uint4 w = make_uint4(0, 0, 0, 0);
+      uint4 x = w[p];
       if (n < Nk) {
-        w = *reinterpret_cast<const uint4*>(src + (int64_t)n * k_sn);
-        w.x = pack_bf16(bf16_lo(w.x) - mean[0], bf16_hi(w.x) - mean[1]);
-        w.y = pack_bf16(bf16_lo(w.y) - mean[2], bf16_hi(w.y) - mean[3]);
-        w.z = pack_bf16(bf16_lo(w.z) - mean[4], bf16_hi(w.z) - mean[5]);
-        w.w = pack_bf16(bf16_lo(w.w) - mean[6], bf16_hi(w.w) - mean[7]);
+        x.x = pack_bf16(bf16_lo(x.x) - mean[0], bf16_hi(x.x) - mean[1]);
+        x.y = pack_bf16(bf16_lo(x.y) - mean[2], bf16_hi(x.y) - mean[3]);
+        x.z = pack_bf16(bf16_lo(x.z) - mean[4], bf16_hi(x.z) - mean[5]);
+        x.w = pack_bf16(bf16_lo(x.w) - mean[6], bf16_hi(x.w) - mean[7]);
       }
-      *reinterpret_cast<uint4*>(&ks[r * PITCH + c * 8]) = w;
+      *reinterpret_cast<uint4*>(&ks[r * PITCH + c * 8]) = x;
     }
   }
   __syncthreads();
 
-  const int M = G * Tq;
   const uint32_t* ks32 = reinterpret_cast<const uint32_t*>(ks);
   for (int m0 = warp * 16; m0 < M; m0 += 8 * 16) {
-    // A fragments: rows m0+g and m0+g+8 of the stacked block means of this GQA group
     uint32_t a[D / 16][4];
-    const int r0 = m0 + g, r1 = m0 + g + 8;
-    const uint32_t* p0 = nullptr; const uint32_t* p1 = nullptr;
-    if (r0 < M) p0 = reinterpret_cast<const uint32_t*>(qm + (((int64_t)b * Hq + hkv * G + r0 / Tq) * Tq + r0 % Tq) * D);
-    if (r1 < M) p1 = reinterpret_cast<const uint32_t*>(qm + (((int64_t)b * Hq + hkv * G + r1 / Tq) * Tq + r1 % Tq) * D);
 #pragma unroll
-    for (int s = 0; s < D / 16; ++s) {
-      a[s][0] = p0 ? p0[s * 8 + tg] : 0u;
-      a[s][1] = p1 ? p1[s * 8 + tg] : 0u;
-      a[s][2] = p0 ? p0[s * 8 + 4 + tg] : 0u;
-      a[s][3] = p1 ? p1[s * 8 + 4 + tg] : 0u;
-    }
+    for (int s = 0; s < D / 16; ++s)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[s][i] = a_next[s][i];
+    if (m0 + 8 * 16 < M) load_a(a_next, m0 + 8 * 16);
     __nv_bfloat16* cw = cs + warp * (16 * 136);
 #pragma unroll 4
     for (int nt = 0; nt < 16; ++nt) {

@@ -126,7 +126,8 @@ def test_reference_llama_fixtures(tag):
 
 def test_varlen_matches_per_sequence_calls():
     Hq, Hkv, D = 4, 2, 128
-    lens_q, lens_k = [100, 257, 1, 64], [130, 257, 40, 64]
+    # a run of three equal-length neighbours (one batched launch), ragged ones, a sequence without keys
+    lens_q, lens_k = [100, 257, 200, 200, 200, 1, 64, 5], [130, 257, 300, 300, 300, 40, 64, 0]
     g = torch.Generator().manual_seed(0)
     q = torch.randn(sum(lens_q), Hq, D, generator=g).to(torch.bfloat16).to(DEV)
     k = (torch.randn(sum(lens_k), Hkv, D, generator=g) + 1.5).to(torch.bfloat16).to(DEV)
@@ -137,6 +138,11 @@ def test_varlen_matches_per_sequence_calls():
     assert out.shape == q.shape
     for i in range(len(lens_q)):
         qs, ks = slice(int(cq[i]), int(cq[i + 1])), slice(int(ck[i]), int(ck[i + 1]))
+        if lens_k[i] == 0:
+            assert float(out[qs].float().abs().max()) == 0.0
+            continue
+        one = sa.sageattn(q[qs][None], k[ks][None], v[ks][None], tensor_layout="NHD", is_causal=True)[0]
+        assert torch.equal(out[qs], one)                       # batching and streams change nothing
         ref = sage3.sdpa_fp32(q[qs].cpu().transpose(0, 1)[None], k[ks].cpu().transpose(0, 1)[None],
                               v[ks].cpu().transpose(0, 1)[None], is_causal=True)[0].transpose(0, 1)
         cos, _ = sage3.accuracy(out[qs].float().cpu(), ref)

@@ -92,3 +92,19 @@ def test_custom_op_fake_needs_no_gpu():
     out = compile_ops.sageattn_compilable(q.transpose(1, 2), k.transpose(1, 2), k.transpose(1, 2), tensor_layout="NHD",
                                           k_packing=True)
     assert out.shape == (2, 300, 8, 128)
+
+
+def test_packed_length_helpers_match_reference_formulas():
+    """sage3_packed_len = the key-length fix-up of sageattn4/api.py:267-274; sage3_packed_rows = rows of the
+    packed tensors (groups of 15 tokens padded, 16 slots each, api.py:124-127,146)."""
+    from oracle import sage3
+    lib = _lib.load()
+    for n in (1, 14, 15, 16, 29, 30, 31, 100, 128, 8192, 32760, 75600):
+        q = 15
+        want = n // q * (q + 1) if n % q == 0 else n // q * (q + 1) + 1 + n % q
+        assert lib.sage3_packed_len(n) == want == sage3.logical_to_packed_len(n)
+        assert lib.sage3_packed_rows(n) == 16 * ((n + 14) // 15)
+        assert lib.sage3_packed_rows(n) - 14 <= lib.sage3_packed_len(n) <= lib.sage3_packed_rows(n)
+    assert lib.sage3_packed_len(0) == 0 and lib.sage3_packed_rows(-3) == 0
+    a = _lib.PackArgs()
+    assert lib.sage3_pack_kv(C.byref(a), None) == _lib.ERR_ARGUMENT       # null tensors: refused before any CUDA call

@@ -102,3 +102,18 @@ def test_packed_mode_rejects_unsupported_variants():
         sa.sageattn4_blackwell(q, k, v, per_block_mean=False)
     with pytest.raises(AssertionError):
         sa.sageattn4_blackwell(q, k, v, quant_block=8)
+
+
+@pytest.mark.parametrize("tag", ["s128", "s256"])
+def test_packed_operator_on_reference_fixtures(tag):
+    """The reference's real-activation inputs (tests/fixtures/*.pt) with its own thresholds against fp32 SDPA
+    (tests/test.py:36-47: 1 - cos < 0.01, L1 < 0.01), K-packing operator."""
+    from pathlib import Path
+    z = np.load(Path(__file__).resolve().parent / "golden" / "llama_fixture_qkv.npz")
+    bf = lambda name: torch.from_numpy(nvfp4.from_bf16_bits(z[f"{tag}_{name}"])).to(torch.bfloat16).to(DEV)
+    q, k, v = bf("q"), bf("k"), bf("v")
+    out = sa.sageattn4_blackwell(q, k, v, is_causal=False, check_status=True).float().cpu()
+    ref = torch.from_numpy(z[f"{tag}_sdpa"])
+    cos = torch.nn.functional.cosine_similarity(out, ref, dim=-1).mean().item()
+    l1 = torch.nn.functional.l1_loss(out, ref).item()
+    assert 1 - cos < 0.01 and l1 < 0.01, (cos, l1)
