@@ -13,6 +13,8 @@ reference's video-model activations):
   dit      B=1 H=40 N=32760 D=128 non-causal, K channel offsets ~N(0,4), 5% of V channels x8  (default)
   prefill  B=4 Hq=32 Hkv=8 N=8192 D=128 causal, K channel offsets ~N(0,2)
   ulysses  B=1 H=40 N=75600 D=128 non-causal, sequence-sharded input, all-to-all over NCCL (needs N>1)
+  ring     the same problem, K/V shards passed round a ring of point-to-point copies, partial outputs merged
+           by their log-sum-exp (needs N>1)
 With N GPUs the `dit` / `prefill` workloads are sharded over batch x heads with no collective: every
 rank processes the same per-GPU workload (weak scaling) and the value is the sum over ranks.
 """
@@ -37,6 +39,7 @@ WORKLOADS = {
     "dit": dict(B=1, Hq=40, Hkv=40, N=32760, D=128, causal=False, k_off=2.0, v_out=0.05),
     "prefill": dict(B=4, Hq=32, Hkv=8, N=8192, D=128, causal=True, k_off=math.sqrt(2.0), v_out=0.0),
     "ulysses": dict(B=1, Hq=40, Hkv=40, N=75600, D=128, causal=False, k_off=2.0, v_out=0.0),
+    "ring": dict(B=1, Hq=40, Hkv=40, N=75600, D=128, causal=False, k_off=2.0, v_out=0.0),
     "profile": dict(B=1, Hq=10, Hkv=10, N=32760, D=128, causal=False, k_off=2.0, v_out=0.05),   # a quarter of dit
     "small": dict(B=1, Hq=8, Hkv=8, N=1024, D=128, causal=False, k_off=2.0, v_out=0.0),
 }
@@ -240,11 +243,11 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
 
-    if args.workload == "ulysses":
+    if args.workload in ("ulysses", "ring"):
         from sageattention_b200 import distributed as sd
         if world < 2:
-            raise SystemExit("the ulysses workload needs >= 2 GPUs (torchrun)")
-        return sd.bench_ulysses(args, w, dist, dev)
+            raise SystemExit("the ulysses and ring workloads need >= 2 GPUs (torchrun)")
+        return sd.bench_ulysses(args, w, dist, dev, ring=(args.workload == "ring"))
 
     B, Hq, Hkv, N, D, causal = w["B"], w["Hq"], w["Hkv"], w["N"], w["D"], w["causal"]
     q, k, v = gen_inputs(w, seed=1234 + rank, device=dev)

@@ -196,15 +196,15 @@ def ring_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group=None
 
 
 # ----------------------------------------------------------------------------------------------------
-# benchmark leg used by bench.py --workload ulysses
+# benchmark leg used by bench.py --workload ulysses / ring
 # ----------------------------------------------------------------------------------------------------
 
-def bench_ulysses(args, w, dist_mod, dev):
+def bench_ulysses(args, w, dist_mod, dev, ring: bool = False):
     import json
     import sageattention_b200 as sa
     rank, world = dist_mod.get_rank(), dist_mod.get_world_size()
     B, H, N, D = w["B"], w["Hq"], w["N"], w["D"]
-    if H % world or N % world:
+    if N % world or (H % world and not ring):
         raise SystemExit("ulysses workload: heads and tokens must be multiples of the number of GPUs")
     n = N // world
     g = torch.Generator(device=dev).manual_seed(4321 + rank)
@@ -215,6 +215,8 @@ def bench_ulysses(args, w, dist_mod, dev):
     chunks = 2 if (H // world) % 2 == 0 else 1
 
     def step():
+        if ring:
+            return ring_attention(q, k, v, is_causal=w["causal"])
         return ulysses_attention(q, k, v, head_chunks=chunks, is_causal=w["causal"])
 
     for _ in range(max(args.warmup, 3)):
@@ -238,8 +240,12 @@ def bench_ulysses(args, w, dist_mod, dev):
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "fp4 (e2m1 x ue4m3 block-scaled, fp32 accumulate)",
             "data": "synthetic",
-            "config": {"workload": "ulysses", "B": B, "H": H, "N": N, "D": D, "causal": w["causal"],
-                       "sharding": f"sequence-sharded input, all-to-all to {H // world} heads per GPU, {chunks} head chunk(s)",
-                       "step": "3 all-to-all + K mean + fused quant + delta_s + attention + 1 all-to-all"},
-            "gpu_launches": 4 * chunks * args.steps}), flush=True)
+            "config": ({"workload": "ring", "B": B, "H": H, "N": N, "D": D, "causal": w["causal"],
+                        "sharding": f"sequence-sharded input, {world} ring steps of {n} keys, K/V shards by point-to-point copies",
+                        "step": f"{world} x (K mean + fused quant + delta_s + attention) + {world - 1} K/V exchanges + LSE merges"}
+                       if ring else
+                       {"workload": "ulysses", "B": B, "H": H, "N": N, "D": D, "causal": w["causal"],
+                        "sharding": f"sequence-sharded input, all-to-all to {H // world} heads per GPU, {chunks} head chunk(s)",
+                        "step": "3 all-to-all + K mean + fused quant + delta_s + attention + 1 all-to-all"}),
+            "gpu_launches": 4 * (world if ring else chunks) * args.steps}), flush=True)
     dist_mod.destroy_process_group()
