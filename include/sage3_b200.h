@@ -146,6 +146,25 @@ typedef struct {
   size_t scratch_bytes;
 } sage3_pack_args;
 
+/* Variable-length batch (the calling convention of sageattn_varlen, sageattention/core.py:334-358): packed
+ * bf16 [tokens, heads, D] tensors and int32 prefix sums of the sequence lengths on the device. */
+typedef struct {
+  sage3_shape shape;          /* B = number of sequences; Nq, Nk = the LONGEST query / key sequence
+                                 (max_seqlen_q, max_seqlen_k): they size the workspace                   */
+  const void *q, *k, *v;      /* [sum(len_q), Hq, D], [sum(len_k), Hkv, D] x 2                           */
+  int64_t q_stride_n, q_stride_h, k_stride_n, k_stride_h, v_stride_n, v_stride_h;   /* elements        */
+  const int32_t* cu_seqlens_q; /* device int32 [B+1], starts at 0                                        */
+  const int32_t* cu_seqlens_k;
+  void* out;                  /* bf16 [sum(len_q), Hq, D], strides below                                 */
+  int64_t out_stride_n, out_stride_h;
+  float sm_scale;             /* <= 0: head_dim^-0.5                                                     */
+  int32_t is_causal;          /* bottom-right aligned per sequence                                       */
+  int32_t smooth_k;           /* K channel means are taken per sequence                                  */
+  void* workspace;            /* >= sage3_buffer_sizes(shape, 1).workspace bytes, 256-byte aligned       */
+  size_t workspace_bytes;
+  int32_t* device_status;     /* optional, as in sage3_fwd_args                                          */
+} sage3_varlen_args;
+
 SAGE3_API int sage3_version(void);
 SAGE3_API const char* sage3_status_string(int status);
 /* cudaError_t of the most recent failing CUDA call made by this thread inside the library. */
@@ -156,6 +175,12 @@ SAGE3_API int sage3_buffer_sizes(const sage3_shape* shape, int per_block_mean, s
 SAGE3_API int sage3_quant_qkv(const sage3_quant_args* args, void* stream);
 SAGE3_API int sage3_attn_fwd(const sage3_attn_args* args, void* stream);
 SAGE3_API int sage3_attention(const sage3_fwd_args* args, void* stream);
+/* sage3_attention for a variable-length batch in ONE pass over the same four kernels: every kernel takes
+ * the sequence offsets and lengths from cu_seqlens_*, the operands are laid out as for a [B, longest] batch
+ * and tiles beyond a sequence's end cost nothing.  Replaces the per-sequence loop a caller of the dense
+ * entry points would write; the reference's own varlen operator (sageattention/core.py:334-448) belongs to
+ * its INT8 kernels and only lends the calling convention.  Per-block Q mean, no LSE output. */
+SAGE3_API int sage3_attention_varlen(const sage3_varlen_args* args, void* stream);
 /* K-packing mode.  sage3_pack_kv replaces quant_pack_k / quant_pack_v and the K centring of api.py:122-177,
  * 184, 193-194 (eager PyTorch in the reference); its outputs go through sage3_quant_qkv with
  * shape.Nk = sage3_packed_rows(Nk) and smooth_k = 0.  sage3_attn_fwd_packed is sage3_attn_fwd with the

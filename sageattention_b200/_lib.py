@@ -65,10 +65,20 @@ class PackArgs(C.Structure):
                 ("k_lambda", C.c_void_p), ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t)]
 
 
+class VarlenArgs(C.Structure):
+    _fields_ = [("shape", Shape), ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p),
+                ("q_stride_n", C.c_int64), ("q_stride_h", C.c_int64), ("k_stride_n", C.c_int64),
+                ("k_stride_h", C.c_int64), ("v_stride_n", C.c_int64), ("v_stride_h", C.c_int64),
+                ("cu_seqlens_q", C.c_void_p), ("cu_seqlens_k", C.c_void_p),
+                ("out", C.c_void_p), ("out_stride_n", C.c_int64), ("out_stride_h", C.c_int64),
+                ("sm_scale", C.c_float), ("is_causal", C.c_int32), ("smooth_k", C.c_int32),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("device_status", C.c_void_p)]
+
+
 EXPORTS = ("sage3_version", "sage3_status_string", "sage3_last_cuda_error", "sage3_buffer_sizes",
            "sage3_quant_qkv", "sage3_attn_fwd", "sage3_attention", "sage3_read_device_status",
            "sage3_k_mean_static", "sage3_packed_rows", "sage3_packed_len", "sage3_pack_kv",
-           "sage3_attn_fwd_packed")
+           "sage3_attn_fwd_packed", "sage3_attention_varlen")
 
 _lib = None
 
@@ -96,6 +106,7 @@ def load() -> C.CDLL:
     lib.sage3_packed_len.argtypes = [C.c_int]
     lib.sage3_pack_kv.argtypes = [C.POINTER(PackArgs), C.c_void_p]
     lib.sage3_attn_fwd_packed.argtypes = [C.POINTER(AttnArgs), C.c_void_p, C.c_void_p]
+    lib.sage3_attention_varlen.argtypes = [C.POINTER(VarlenArgs), C.c_void_p]
     for name in EXPORTS:
         getattr(lib, name)            # raises AttributeError if an export is missing
     _lib = lib

@@ -320,69 +320,58 @@ def sageattn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: s
 
 def sageattn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q: torch.Tensor,
                     cu_seqlens_k: torch.Tensor, max_seqlen_q: int, max_seqlen_k: int, is_causal: bool = False,
-                    sm_scale: Optional[float] = None, smooth_k: bool = True, **kwargs) -> torch.Tensor:
+                    sm_scale: Optional[float] = None, smooth_k: bool = True, check_status: bool = False,
+                    **kwargs) -> torch.Tensor:
     """Variable-length batch (``sageattention/core.py:334-448``): q ``[sum(len_q), Hq, D]``, k/v
-    ``[sum(len_k), Hkv, D]``, ``cu_seqlens_*`` the int32 prefix sums (length batch + 1).  Each sequence
-    is smoothed, quantised and attended on its own (K means never mix sequences); neighbouring sequences of
-    equal length share one batched launch."""
+    ``[sum(len_k), Hkv, D]``, ``cu_seqlens_*`` the int32 prefix sums (length batch + 1, on the device).
+    One pass over the four kernels for the whole batch (``sage3_attention_varlen``); every sequence is
+    smoothed, quantised and attended on its own (K means never mix sequences); sequences without keys give
+    zeros.  ``max_seqlen_*`` must bound the longest sequence - they size the workspace."""
+    lib = _lib.load()
     if q.dim() != 3 or k.dim() != 3 or v.dim() != 3:
         raise ValueError("varlen tensors must be [tokens, heads, head_dim]")
-    cq = cu_seqlens_q.tolist()
-    ck = cu_seqlens_k.tolist()
-    if len(cq) != len(ck) or cq[0] != 0 or ck[0] != 0:
-        raise ValueError("cu_seqlens_q and cu_seqlens_k must both start at 0 and have batch + 1 entries")
-    out = torch.empty_like(q)
-    nseq = len(cq) - 1
-    # runs of neighbouring sequences with equal lengths are one batched call (a view, no copy); different
-    # runs go to a small pool of streams so that the kernels of short sequences, which cannot fill the GPU
-    # on their own, overlap
-    runs = []
-    i = 0
-    while i < nseq:
-        lq, lk = cq[i + 1] - cq[i], ck[i + 1] - ck[i]
-        if lq > max_seqlen_q or lk > max_seqlen_k:
-            raise ValueError("sequence longer than max_seqlen")
-        j = i + 1
-        while j < nseq and cq[j + 1] - cq[j] == lq and ck[j + 1] - ck[j] == lk:
-            j += 1
-        runs.append((i, j, lq, lk))
-        i = j
+    _check_device(q)
+    for t in (q, k, v):
+        if t.dtype != torch.bfloat16:
+            raise AssertionError("TODO: support inputs other than bfloat16")
+        if t.stride(-1) != 1:
+            raise ValueError("the head dimension must be contiguous")
+    nseq = cu_seqlens_q.numel() - 1
+    if cu_seqlens_k.numel() != nseq + 1 or nseq < 1:
+        raise ValueError("cu_seqlens_q and cu_seqlens_k must both have batch + 1 entries")
+    if max_seqlen_q <= 0 or max_seqlen_k <= 0:
+        raise ValueError("max_seqlen_q and max_seqlen_k must be positive")
     dev = q.device
-    work = [r for r in runs if r[2] > 0 and r[3] > 0]
-    for (a, b, lq, lk) in runs:
-        if lq > 0 and lk == 0:
-            out[cq[a]:cq[b]].zero_()
-    use_pool = len(work) > 1
-    if use_pool:
-        if dev not in _varlen_streams:
-            _varlen_streams[dev] = tuple(torch.cuda.Stream(dev) for _ in range(4))
-        cur = torch.cuda.current_stream(dev)
-        fork = torch.cuda.Event()
-        fork.record(cur)
-    for n, (a, b, lq, lk) in enumerate(work):
-        H, Hk, D = q.shape[1], k.shape[1], q.shape[2]
-        qi = q[cq[a]:cq[b]].view(b - a, lq, H, D)
-        ki = k[ck[a]:ck[b]].view(b - a, lk, Hk, D)
-        vi = v[ck[a]:ck[b]].view(b - a, lk, Hk, D)
-        st = _varlen_streams[dev][n % 4] if use_pool else torch.cuda.current_stream(dev)
-        with torch.cuda.stream(st):
-            if use_pool:
-                st.wait_event(fork)
-            oi = sageattn3_blackwell(qi, ki, vi, tensor_layout="NHD", is_causal=is_causal, sm_scale=sm_scale,
-                                     smooth_k=smooth_k, **kwargs)
-            out[cq[a]:cq[b]] = oi.view(-1, H, D)
-            if use_pool:
-                oi.record_stream(st)
-    if use_pool:
-        for st in _varlen_streams[dev]:
-            ev = torch.cuda.Event()
-            ev.record(st)
-            cur.wait_event(ev)
+    cq = cu_seqlens_q.to(device=dev, dtype=torch.int32).contiguous()
+    ck = cu_seqlens_k.to(device=dev, dtype=torch.int32).contiguous()
+    Hq, D = q.shape[1], q.shape[2]
+    Hkv = k.shape[1]
+    if Hq % Hkv != 0 or v.shape != k.shape or k.shape[2] != D:
+        raise ValueError("q, k, v shapes do not match")
+    out = torch.empty_like(q)
+    z = buffer_sizes(nseq, Hq, Hkv, int(max_seqlen_q), int(max_seqlen_k), D, 1)
+    ws = torch.empty(int(z.workspace), dtype=torch.uint8, device=dev)
+    status = torch.empty(1, dtype=torch.int32, device=dev)
+    a = _lib.VarlenArgs()
+    a.shape = _lib.Shape(nseq, Hq, Hkv, int(max_seqlen_q), int(max_seqlen_k), D)
+    a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    a.q_stride_n, a.q_stride_h = q.stride(0), q.stride(1)
+    a.k_stride_n, a.k_stride_h = k.stride(0), k.stride(1)
+    a.v_stride_n, a.v_stride_h = v.stride(0), v.stride(1)
+    a.cu_seqlens_q, a.cu_seqlens_k = cq.data_ptr(), ck.data_ptr()
+    a.out, a.out_stride_n, a.out_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
+    a.sm_scale = float(sm_scale) if sm_scale is not None else 0.0
+    a.is_causal, a.smooth_k = int(bool(is_causal)), int(bool(smooth_k))
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    a.device_status = status.data_ptr()
+    with torch.cuda.device(dev):
+        _lib.check(lib.sage3_attention_varlen(C.byref(a), _stream_ptr(dev)), "sage3_attention_varlen")
+        if check_status:
+            _lib.check(lib.sage3_read_device_status(status.data_ptr(), _stream_ptr(dev), None), "attention kernel")
     return out
 
 
 _host_streams = {}
-_varlen_streams = {}
 
 
 def sageattn_from_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[torch.Tensor] = None,

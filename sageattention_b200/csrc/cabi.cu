@@ -84,7 +84,7 @@ int sage3_buffer_sizes(const sage3_shape* shape, int per_block_mean, sage3_sizes
   return SAGE3_OK;
 }
 
-int sage3_quant_qkv(const sage3_quant_args* a, void* stream_) {
+static int quant_qkv_impl(const sage3_quant_args* a, const int* cu_q, const int* cu_k, void* stream_) {
   if (a == nullptr) return SAGE3_ERR_ARGUMENT;
   if (int st = check_shape(a->shape)) return st;
   if (int st = check_tensor(a->q)) return st;
@@ -106,7 +106,7 @@ int sage3_quant_qkv(const sage3_quant_args* a, void* stream_) {
       if (!a->km || !a->scratch || !aligned16(a->scratch)) return SAGE3_ERR_ARGUMENT;
       if (a->scratch_bytes < sage3::quant_scratch_bytes(s.B, s.Hkv, s.Nk, s.D)) return SAGE3_ERR_ARGUMENT;
       cudaError_t e = sage3::launch_channel_mean(a->k.ptr, a->k.stride_b, a->k.stride_h, a->k.stride_n, s.B, s.Hkv,
-                                                 s.Nk, s.D, (float)s.Nk, a->scratch, a->km, stream);
+                                                 s.Nk, s.D, (float)s.Nk, a->scratch, a->km, stream, cu_k);
       if (e != cudaSuccess) return cuda_fail(e);
       km = a->km;
     }
@@ -117,6 +117,7 @@ int sage3_quant_qkv(const sage3_quant_args* a, void* stream_) {
     if (!a->scratch || a->scratch_bytes < sage3::quant_scratch_bytes(s.B, s.Hq, s.Nq, s.D)) return SAGE3_ERR_ARGUMENT;
     cudaError_t e = sage3::launch_channel_mean(a->q.ptr, a->q.stride_b, a->q.stride_h, a->q.stride_n, s.B, s.Hq, s.Nq,
                                                s.D, (float)(Tq * 128), a->scratch, a->qm, stream);
+    if (cu_q != nullptr) return SAGE3_ERR_UNSUPPORTED;   // whole-sequence Q mean is not built for packed batches
     if (e != cudaSuccess) return cuda_fail(e);
   }
 
@@ -132,6 +133,7 @@ int sage3_quant_qkv(const sage3_quant_args* a, void* stream_) {
   q.qm_override = a->per_block_mean == 1 ? a->qm_in : nullptr;
   q.q_codes = a->q_codes; q.q_sf = a->q_sf; q.k_codes = a->k_codes; q.k_sf = a->k_sf;
   q.vt_codes = a->vt_codes; q.vt_sf = a->vt_sf; q.qm = a->qm;
+  q.cu_q = cu_q; q.cu_k = cu_k;
   cudaError_t e = sage3::launch_quant_qkv(q, stream);
   if (e != cudaSuccess) return cuda_fail(e);
 
@@ -139,7 +141,7 @@ int sage3_quant_qkv(const sage3_quant_args* a, void* stream_) {
     if (!a->q.ptr || !a->k.ptr || a->per_block_mean < 0) return SAGE3_ERR_ARGUMENT;
     sage3::DeltaSArgs d{};
     d.qm = a->qm; d.k = a->k.ptr; d.k_sb = a->k.stride_b; d.k_sh = a->k.stride_h; d.k_sn = a->k.stride_n;
-    d.km = km; d.ds = a->delta_s;
+    d.km = km; d.ds = a->delta_s; d.cu_k = cu_k;
     d.B = s.B; d.Hq = s.Hq; d.Hkv = s.Hkv; d.Tq = a->per_block_mean == 1 ? Tq : 1; d.Nk = s.Nk; d.D = s.D;
     e = sage3::launch_delta_s(d, stream);
     if (e != cudaSuccess) return cuda_fail(e);
@@ -147,7 +149,9 @@ int sage3_quant_qkv(const sage3_quant_args* a, void* stream_) {
   return SAGE3_OK;
 }
 
-static int attn_fwd_impl(const sage3_attn_args* a, const float* k_lambda, void* stream_) {
+int sage3_quant_qkv(const sage3_quant_args* a, void* stream) { return quant_qkv_impl(a, nullptr, nullptr, stream); }
+
+static int attn_fwd_impl(const sage3_attn_args* a, const float* k_lambda, const int* cu_q, const int* cu_k, void* stream_) {
   if (a == nullptr) return SAGE3_ERR_ARGUMENT;
   if (int st = check_shape(a->shape)) return st;
   if (!a->q_codes || !a->q_sf || !a->k_codes || !a->k_sf || !a->vt_codes || !a->vt_sf || !a->out || !a->device_status)
@@ -170,16 +174,17 @@ static int attn_fwd_impl(const sage3_attn_args* a, const float* k_lambda, void* 
   k.B = s.B; k.Hq = s.Hq; k.Hkv = s.Hkv; k.Nq = s.Nq; k.Nk = s.Nk; k.D = s.D;
   k.sm_scale = a->sm_scale; k.causal = a->is_causal;
   k.k_lambda = k_lambda;
+  k.cu_q = cu_q; k.cu_k = cu_k;
   e = sage3::launch_attn_fwd(k, stream);
   if (e != cudaSuccess) return cuda_fail(e);
   return SAGE3_OK;
 }
 
-int sage3_attn_fwd(const sage3_attn_args* a, void* stream) { return attn_fwd_impl(a, nullptr, stream); }
+int sage3_attn_fwd(const sage3_attn_args* a, void* stream) { return attn_fwd_impl(a, nullptr, nullptr, nullptr, stream); }
 
 int sage3_attn_fwd_packed(const sage3_attn_args* a, const float* k_lambda, void* stream) {
   if (k_lambda == nullptr || !aligned16(k_lambda)) return SAGE3_ERR_ARGUMENT;
-  return attn_fwd_impl(a, k_lambda, stream);
+  return attn_fwd_impl(a, k_lambda, nullptr, nullptr, stream);
 }
 
 int sage3_packed_rows(int nk) { return nk <= 0 ? 0 : 16 * ((nk + 14) / 15); }
@@ -250,6 +255,42 @@ int sage3_attention(const sage3_fwd_args* a, void* stream) {
   t.out = a->out; t.out_stride_b = a->out_stride_b; t.out_stride_h = a->out_stride_h; t.out_stride_n = a->out_stride_n;
   t.lse = a->lse; t.sm_scale = sm_scale; t.is_causal = a->is_causal; t.device_status = status;
   return sage3_attn_fwd(&t, stream);
+}
+
+int sage3_attention_varlen(const sage3_varlen_args* a, void* stream) {
+  if (a == nullptr || a->workspace == nullptr || a->out == nullptr) return SAGE3_ERR_ARGUMENT;
+  if (!a->q || !a->k || !a->v || !a->cu_seqlens_q || !a->cu_seqlens_k) return SAGE3_ERR_ARGUMENT;
+  if ((a->out_stride_h % 8) || (a->out_stride_n % 8)) return SAGE3_ERR_ARGUMENT;
+  sage3_sizes z;
+  if (int st = sage3_buffer_sizes(&a->shape, 1, &z)) return st;
+  if (a->workspace_bytes < z.workspace || (reinterpret_cast<uintptr_t>(a->workspace) & 255)) return SAGE3_ERR_ARGUMENT;
+  char* w = reinterpret_cast<char*>(a->workspace);
+  auto take = [&](size_t n) { char* p = w; w += align256(n); return (void*)p; };
+  sage3_quant_args q{};
+  q.shape = a->shape;
+  q.q.ptr = a->q; q.q.stride_b = 0; q.q.stride_h = a->q_stride_h; q.q.stride_n = a->q_stride_n;
+  q.k.ptr = a->k; q.k.stride_b = 0; q.k.stride_h = a->k_stride_h; q.k.stride_n = a->k_stride_n;
+  q.v.ptr = a->v; q.v.stride_b = 0; q.v.stride_h = a->v_stride_h; q.v.stride_n = a->v_stride_n;
+  q.per_block_mean = 1; q.smooth_k = a->smooth_k;
+  q.q_codes = take(z.q_codes); q.q_sf = take(z.q_sf); q.k_codes = take(z.k_codes); q.k_sf = take(z.k_sf);
+  q.vt_codes = take(z.vt_codes); q.vt_sf = take(z.vt_sf);
+  q.qm = take(z.qm);
+  q.km = take(z.km);
+  q.delta_s = take(z.delta_s);
+  q.scratch = take(z.scratch); q.scratch_bytes = z.scratch;
+  int32_t* status = reinterpret_cast<int32_t*>(take(4));
+  if (a->device_status) status = a->device_status;
+  if (int st = quant_qkv_impl(&q, a->cu_seqlens_q, a->cu_seqlens_k, stream)) return st;
+  sage3_attn_args t{};
+  t.shape = a->shape;
+  t.q_codes = q.q_codes; t.q_sf = q.q_sf; t.k_codes = q.k_codes; t.k_sf = q.k_sf; t.vt_codes = q.vt_codes; t.vt_sf = q.vt_sf;
+  t.delta_s = q.delta_s;
+  t.delta_s_rows = (a->shape.Nq + 127) / 128;
+  t.out = a->out; t.out_stride_b = 0; t.out_stride_h = a->out_stride_h; t.out_stride_n = a->out_stride_n;
+  t.lse = nullptr;
+  t.sm_scale = a->sm_scale > 0.f ? a->sm_scale : 1.0f / sqrtf((float)a->shape.D);
+  t.is_causal = a->is_causal; t.device_status = status;
+  return attn_fwd_impl(&t, nullptr, a->cu_seqlens_q, a->cu_seqlens_k, stream);
 }
 
 int sage3_k_mean_static(const sage3_shape* shape, const sage3_tensor* k, void* km_out, void* stream) {

@@ -20,7 +20,7 @@ template <int D>
 __global__ void __launch_bounds__(256, 3) delta_s_kernel(
     const __nv_bfloat16* __restrict__ qm, const __nv_bfloat16* __restrict__ k, int64_t k_sb, int64_t k_sh,
     int64_t k_sn, const __nv_bfloat16* __restrict__ km, __nv_bfloat16* __restrict__ ds, int Hq, int Hkv, int Tq,
-    int Nk, int Nk_pad) {
+    int Nk, int Nk_pad, const int* __restrict__ cu_k) {
   constexpr int PITCH = D + 8;                         // bf16 elements; 4-bank skew per row
   extern __shared__ __align__(16) unsigned char dyn_smem[];
   __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(dyn_smem);              // [128][PITCH]
@@ -57,7 +57,9 @@ __global__ void __launch_bounds__(256, 3) delta_s_kernel(
       mean[0] = bf16_lo(m.x); mean[1] = bf16_hi(m.x); mean[2] = bf16_lo(m.y); mean[3] = bf16_hi(m.y);
       mean[4] = bf16_lo(m.z); mean[5] = bf16_hi(m.z); mean[6] = bf16_lo(m.w); mean[7] = bf16_hi(m.w);
     }
-    const __nv_bfloat16* src = k + b * k_sb + hkv * k_sh + c * 8;
+    // variable-length batch: sequence b starts at token cu_k[b] of the packed tensor and has its own length
+    if (cu_k != nullptr) Nk = cu_k[b + 1] - cu_k[b];
+    const __nv_bfloat16* src = k + (cu_k ? (int64_t)cu_k[b] * k_sn : b * k_sb) + hkv * k_sh + c * 8;
     uint4 w[128 / RPP];
 #pragma unroll
     for (int p = 0; p < 128 / RPP; ++p) {                  // all loads in flight before the first use
@@ -129,11 +131,11 @@ cudaError_t launch_delta_s(const DeltaSArgs& a, cudaStream_t stream) {
   if (a.D == 128)
     delta_s_kernel<128><<<grid, 256, smem, stream>>>((const __nv_bfloat16*)a.qm, (const __nv_bfloat16*)a.k, a.k_sb, a.k_sh,
                                                   a.k_sn, (const __nv_bfloat16*)a.km, (__nv_bfloat16*)a.ds, a.Hq, a.Hkv,
-                                                  a.Tq, a.Nk, Tk * 128);
+                                                  a.Tq, a.Nk, Tk * 128, a.cu_k);
   else
     delta_s_kernel<64><<<grid, 256, smem, stream>>>((const __nv_bfloat16*)a.qm, (const __nv_bfloat16*)a.k, a.k_sb, a.k_sh,
                                                  a.k_sn, (const __nv_bfloat16*)a.km, (__nv_bfloat16*)a.ds, a.Hq, a.Hkv,
-                                                 a.Tq, a.Nk, Tk * 128);
+                                                 a.Tq, a.Nk, Tk * 128, a.cu_k);
   return cudaGetLastError();
 }
 

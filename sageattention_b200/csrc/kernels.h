@@ -15,11 +15,16 @@ struct QuantArgs {
   const void* q_mean_seq;                 // bf16 [B,Hq,D]   (mode 2)
   const void* qm_override;                // fp32 [B,Hq,Tq,D] or null (mode 1)
   void *q_codes, *q_sf, *k_codes, *k_sf, *vt_codes, *vt_sf, *qm;
+  // variable-length batches: device int32 [B+1] token offsets of the sequences inside packed [tokens, H, D]
+  // tensors (then *_sb is ignored and Nq / Nk are the LONGEST sequence, which sizes the output layouts)
+  const int* cu_q = nullptr;
+  const int* cu_k = nullptr;
 };
 
 size_t quant_scratch_bytes(int B, int H, int N, int D);
 cudaError_t launch_channel_mean(const void* x, int64_t sb, int64_t sh, int64_t sn, int B, int H, int N, int D,
-                                float divisor, void* scratch, void* mean_out, cudaStream_t stream);
+                                float divisor, void* scratch, void* mean_out, cudaStream_t stream,
+                                const int* cu = nullptr);
 cudaError_t launch_quant_qkv(const QuantArgs& a, cudaStream_t stream);
 cudaError_t launch_channel_mean_static(const void* x, int64_t sb, int64_t sh, int64_t sn, int B, int H, int N, int D,
                                        float divisor, void* mean_out, cudaStream_t stream, bool* too_large);
@@ -42,6 +47,7 @@ struct DeltaSArgs {
   const void* km;                         // bf16 [B,Hkv,D] or null
   void* ds;                               // bf16 [B,Hq,Tq,Nk_pad]
   int B, Hq, Hkv, Tq, Nk, D;
+  const int* cu_k = nullptr;              // variable-length batches, see QuantArgs
 };
 cudaError_t launch_delta_s(const DeltaSArgs& a, cudaStream_t stream);
 
@@ -57,6 +63,8 @@ struct AttnArgs {
   float sm_scale;
   int causal;
   const float* k_lambda;                  // K-packing mode: fp32 [B,Hkv,Tk*128]; Nk is then the packed length
+  const int* cu_q = nullptr;              // variable-length batches, see QuantArgs; out is then [tokens, Hq, D]
+  const int* cu_k = nullptr;
 };
 cudaError_t launch_attn_fwd(const AttnArgs& a, cudaStream_t stream);
 

@@ -41,7 +41,7 @@ template <int D>
 __global__ void __launch_bounds__(kThreads) channel_mean_kernel(
     const __nv_bfloat16* __restrict__ x, int64_t sb, int64_t sh, int64_t sn, int H, int N,
     int chunk_tokens, float divisor, float* __restrict__ partial, unsigned int* __restrict__ counters,
-    __nv_bfloat16* __restrict__ mean_out) {
+    __nv_bfloat16* __restrict__ mean_out, const int* __restrict__ cu) {
   constexpr int CH = D / 8;              // 16-byte chunks per row
   constexpr int RPP = kThreads / CH;     // rows per pass
   __shared__ float red[RPP][D];
@@ -49,7 +49,12 @@ __global__ void __launch_bounds__(kThreads) channel_mean_kernel(
   const int bh = blockIdx.y, b = bh / H, h = bh % H;
   const int chunk = blockIdx.x, nchunks = gridDim.x;
   const int t = threadIdx.x, c = t % CH, rl = t / CH;
-  const __nv_bfloat16* base = x + b * sb + h * sh + c * 8;
+  // variable-length batch: sequence b starts at token cu[b] of the packed tensor and has its own length
+  if (cu != nullptr) {
+    N = cu[b + 1] - cu[b];
+    divisor = (float)max(N, 1);
+  }
+  const __nv_bfloat16* base = x + (cu ? (int64_t)cu[b] * sn : b * sb) + h * sh + c * 8;
   const int n0 = chunk * chunk_tokens;
   const int n1 = min(N, n0 + chunk_tokens);
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -138,6 +143,7 @@ struct QuantLaunch {
   uint8_t *q_codes, *q_sf, *k_codes, *k_sf, *vt_codes, *vt_sf;
   __nv_bfloat16* qm;                     // [B,Hq,Tq,D] (mode 1)
   int q_blocks, k_blocks, v_blocks;      // CTAs per role
+  const int *cu_q, *cu_k;                // variable-length batches (else null)
 };
 
 template <int D>
@@ -153,10 +159,16 @@ __global__ void __launch_bounds__(kThreads) quant_qkv_kernel(const QuantLaunch P
     // ----------------------------------------------------------------------------- Q / K roles
     const bool is_q = bid < P.q_blocks;
     if (!is_q) bid -= P.q_blocks;
-    const int T = is_q ? P.Tq : P.Tk, H = is_q ? P.Hq : P.Hkv, N = is_q ? P.Nq : P.Nk;
+    const int T = is_q ? P.Tq : P.Tk, H = is_q ? P.Hq : P.Hkv;
+    int N = is_q ? P.Nq : P.Nk;
     const int tile = bid % T, bh = bid / T, b = bh / H, h = bh % H;
-    const __nv_bfloat16* src = is_q ? P.q + b * P.q_sb + h * P.q_sh : P.k + b * P.k_sb + h * P.k_sh;
     const int64_t sn = is_q ? P.q_sn : P.k_sn;
+    const int* cu = is_q ? P.cu_q : P.cu_k;
+    const __nv_bfloat16* src = is_q ? P.q + b * P.q_sb + h * P.q_sh : P.k + b * P.k_sb + h * P.k_sh;
+    if (cu != nullptr) {                   // sequence b of a packed [tokens, H, D] tensor
+      N = cu[b + 1] - cu[b];
+      src = (is_q ? P.q + h * P.q_sh : P.k + h * P.k_sh) + (int64_t)cu[b] * sn;
+    }
     uint4 w[NP];
 #pragma unroll
     for (int p = 0; p < NP; ++p) {
@@ -261,12 +273,13 @@ __global__ void __launch_bounds__(kThreads) quant_qkv_kernel(const QuantLaunch P
     const int tile = (int)(gt % P.Tk), bh = (int)(gt / P.Tk), b = bh / P.Hkv, h = bh % P.Hkv;
     const int c4 = (warp % WPT) * 4 + (lane >> 3);        // group of 4 channels
     const int blk = lane & 7;                              // 16-token block
-    const __nv_bfloat16* src = P.v + b * P.v_sb + h * P.v_sh + c4 * 4;
+    const __nv_bfloat16* src = P.v + (P.cu_k ? (int64_t)P.cu_k[b] * P.v_sn : b * P.v_sb) + h * P.v_sh + c4 * 4;
+    const int Nv = P.cu_k ? P.cu_k[b + 1] - P.cu_k[b] : P.Nk;
     uint2 x[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const int n = tile * kTile + blk * 16 + i;
-      x[i] = n < P.Nk ? *reinterpret_cast<const uint2*>(src + (int64_t)n * P.v_sn) : make_uint2(0, 0);
+      x[i] = n < Nv ? *reinterpret_cast<const uint2*>(src + (int64_t)n * P.v_sn) : make_uint2(0, 0);
     }
     uint8_t* codes = P.vt_codes + gt * (D * 64);
 #pragma unroll
@@ -322,7 +335,7 @@ size_t quant_scratch_bytes(int B, int H, int N, int D) {
 }
 
 cudaError_t launch_channel_mean(const void* x, int64_t sb, int64_t sh, int64_t sn, int B, int H, int N, int D,
-                                float divisor, void* scratch, void* mean_out, cudaStream_t stream) {
+                                float divisor, void* scratch, void* mean_out, cudaStream_t stream, const int* cu) {
   int chunk = pick_chunk_tokens(N, B * H);
   int nchunks = (N + chunk - 1) / chunk;
   size_t part = (size_t)B * H * nchunks * D * sizeof(float);
@@ -334,10 +347,10 @@ cudaError_t launch_channel_mean(const void* x, int64_t sb, int64_t sh, int64_t s
   dim3 grid(nchunks, B * H);
   if (D == 128)
     channel_mean_kernel<128><<<grid, kThreads, 0, stream>>>((const __nv_bfloat16*)x, sb, sh, sn, H, N, chunk, divisor,
-                                                            partial, counters, (__nv_bfloat16*)mean_out);
+                                                            partial, counters, (__nv_bfloat16*)mean_out, cu);
   else
     channel_mean_kernel<64><<<grid, kThreads, 0, stream>>>((const __nv_bfloat16*)x, sb, sh, sn, H, N, chunk, divisor,
-                                                           partial, counters, (__nv_bfloat16*)mean_out);
+                                                           partial, counters, (__nv_bfloat16*)mean_out, cu);
   return cudaGetLastError();
 }
 
@@ -356,6 +369,7 @@ cudaError_t launch_quant_qkv(const QuantArgs& a, cudaStream_t stream) {
   P.k_codes = (uint8_t*)a.k_codes; P.k_sf = (uint8_t*)a.k_sf;
   P.vt_codes = (uint8_t*)a.vt_codes; P.vt_sf = (uint8_t*)a.vt_sf;
   P.qm = (__nv_bfloat16*)a.qm;
+  P.cu_q = a.cu_q; P.cu_k = a.cu_k;
   P.q_blocks = a.q ? a.B * a.Hq * P.Tq : 0;
   P.k_blocks = a.k ? a.B * a.Hkv * P.Tk : 0;
   const int tpb = a.D == 128 ? 1 : 2;
@@ -415,10 +429,10 @@ cudaError_t launch_channel_mean_static(const void* x, int64_t sb, int64_t sh, in
   dim3 grid(nchunks, B * H);
   if (D == 128)
     channel_mean_kernel<128><<<grid, kThreads, 0, stream>>>((const __nv_bfloat16*)x, sb, sh, sn, H, N, chunk, divisor,
-                                                            partial, counters, (__nv_bfloat16*)mean_out);
+                                                            partial, counters, (__nv_bfloat16*)mean_out, nullptr);
   else
     channel_mean_kernel<64><<<grid, kThreads, 0, stream>>>((const __nv_bfloat16*)x, sb, sh, sn, H, N, chunk, divisor,
-                                                           partial, counters, (__nv_bfloat16*)mean_out);
+                                                           partial, counters, (__nv_bfloat16*)mean_out, nullptr);
   return cudaGetLastError();
 }
 
