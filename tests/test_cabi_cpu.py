@@ -108,3 +108,10 @@ def test_packed_length_helpers_match_reference_formulas():
     assert lib.sage3_packed_len(0) == 0 and lib.sage3_packed_rows(-3) == 0
     a = _lib.PackArgs()
     assert lib.sage3_pack_kv(C.byref(a), None) == _lib.ERR_ARGUMENT       # null tensors: refused before any CUDA call
+
+
+def test_varlen_entry_refuses_bad_arguments_without_a_gpu():
+    lib = _lib.load()
+    a = _lib.VarlenArgs()
+    assert lib.sage3_attention_varlen(C.byref(a), None) == _lib.ERR_ARGUMENT      # no workspace / tensors
+    assert lib.sage3_attention_varlen(None, None) == _lib.ERR_ARGUMENT
