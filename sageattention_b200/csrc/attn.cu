@@ -42,6 +42,26 @@
 #include "common.cuh"
 #include "kernels.h"
 
+// This file is compiled twice: as it is for dense batches, and once more through attn_varlen.cu with
+// SAGE3_VARLEN_BUILD = 1 for variable-length batches (per-sequence offsets and lengths from cu_seqlens).  The
+// dense build sees exactly the code it had before the second one existed: the kernel is paced by its softmax
+// warps and even dead extra code moved their register allocation and timing by a few percent.
+#ifndef SAGE3_VARLEN_BUILD
+#define SAGE3_VARLEN_BUILD 0
+#endif
+// lengths of the sequence a work item `wk` belongs to, inside the softmax warps
+#if SAGE3_VARLEN_BUILD
+#define SEQ_NQ wk.Nq
+#define SEQ_NK wk.Nk
+#define SEQ_NK_LOG wk.Nk
+#define SEQ_TILE_EXISTS (q0 < wk.Nq)
+#else
+#define SEQ_NQ P.Nq
+#define SEQ_NK P.Nk
+#define SEQ_NK_LOG P.Nk_log
+#define SEQ_TILE_EXISTS (qt < P.Tq)
+#endif
+
 namespace sage3 {
 
 namespace {
@@ -123,8 +143,10 @@ struct KParams {
   float scale_log2;      // sm_scale * log2(e)
   const float* lam;      // K-packing mode: lambda per key slot, fp32 [B,Hkv,Tk*128]; Nk is the packed length
   int Nk_log;            // number of key tokens (= Nk unless packed)
-  const int *cu_q, *cu_k; // variable-length batches: token offsets of the sequences (device int32 [B+1]); Nq, Nk,
-                          // Tq, Tk then describe the LONGEST sequence, i.e. the rectangular operand layouts
+#if SAGE3_VARLEN_BUILD
+  const int *cu_q, *cu_k; // token offsets of the sequences (device int32 [B+1]); Nq, Nk, Tq, Tk then describe the
+                          // LONGEST sequence, i.e. the rectangular operand layouts
+#endif
 };
 
 // Bounded wait on an mbarrier phase; also gives up as soon as any CTA has reported a failure.  A failing poll
@@ -327,8 +349,10 @@ __device__ __forceinline__ int packed_len_of(const int len) {
 // One unit of work of a CTA: two adjacent query tiles of one head.
 struct Work {
   int b, hq, hkv, pair;
-  int Nq, Nk, Nk_log;    // lengths of this item's sequence (variable-length batches: its own)
-  int q_base;            // first token of the sequence in the packed output (variable-length batches)
+#if SAGE3_VARLEN_BUILD
+  int Nq, Nk;            // lengths of this item's sequence
+  int q_base;            // first token of the sequence in the packed output
+#endif
   int n_t[2];            // key tiles each query tile visits (0: none / tile does not exist)
   int n_max;
 };
@@ -341,7 +365,7 @@ __device__ __forceinline__ int work_at(const int r, const int total) {
   return w < total ? w : -1;
 }
 
-template <bool kCausal, bool kPacked, bool kVarlen>
+template <bool kCausal, bool kPacked>
 __device__ __forceinline__ Work get_work(const KParams& P, const int w) {
   Work k;
   const int n_pairs = (P.Tq + 1) >> 1;
@@ -360,12 +384,10 @@ __device__ __forceinline__ Work get_work(const KParams& P, const int w) {
   k.b = bh / P.Hq;
   k.hq = bh % P.Hq;
   k.hkv = k.hq / (P.Hq / P.Hkv);
-  k.Nq = P.Nq; k.Nk = P.Nk; k.Nk_log = P.Nk_log; k.q_base = 0;
-  if (kVarlen) {
-    k.q_base = P.cu_q[k.b];
-    k.Nq = P.cu_q[k.b + 1] - k.q_base;
-    k.Nk = k.Nk_log = P.cu_k[k.b + 1] - P.cu_k[k.b];
-  }
+#if SAGE3_VARLEN_BUILD
+  k.q_base = P.cu_q[k.b];
+  k.Nq = P.cu_q[k.b + 1] - k.q_base;
+  k.Nk = P.cu_k[k.b + 1] - P.cu_k[k.b];
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
     const int qt = 2 * k.pair + t;
@@ -375,18 +397,34 @@ __device__ __forceinline__ Work get_work(const KParams& P, const int w) {
       n = Tk;
       if (kCausal) {
         const int q_end = min((qt + 1) * kBlockM, k.Nq);
-        int lim = q_end + k.Nk_log - k.Nq;                 // key tokens [0, lim) can be visible
-        if (kPacked) lim = packed_len_of(lim);             // ... which occupy this many key slots
+        const int lim = q_end + k.Nk - k.Nq;               // key tokens [0, lim) can be visible
         n = lim <= 0 ? 0 : min(Tk, (lim + kBlockN - 1) / kBlockN);
       }
     }
     k.n_t[t] = n;
   }
+#else
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int qt = 2 * k.pair + t;
+    int n = 0;
+    if (qt < P.Tq) {
+      n = P.Tk;
+      if (kCausal) {
+        const int q_end = min((qt + 1) * kBlockM, P.Nq);
+        int lim = q_end + P.Nk_log - P.Nq;                 // key tokens [0, lim) can be visible
+        if (kPacked) lim = packed_len_of(lim);             // ... which occupy this many key slots
+        n = lim <= 0 ? 0 : min(P.Tk, (lim + kBlockN - 1) / kBlockN);
+      }
+    }
+    k.n_t[t] = n;
+  }
+#endif
   k.n_max = max(k.n_t[0], k.n_t[1]);
   return k;
 }
 
-template <int D, bool kCausal, bool kPacked, bool kVarlen>
+template <int D, bool kCausal, bool kPacked>
 __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                                                                    const __grid_constant__ CUtensorMap tm_k,
                                                                    const __grid_constant__ CUtensorMap tm_v,
@@ -466,7 +504,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         uint32_t qn[2] = {0, 0};              // Q tiles loaded so far per slot
         bool ok = true;
         for (int r = 0, w; ok && (w = work_at(r, total_work)) >= 0; ++r) {
-          const Work wk = get_work<kCausal, kPacked, kVarlen>(P, w);
+          const Work wk = get_work<kCausal, kPacked>(P, w);
           int64_t ds_row[2];
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
@@ -524,7 +562,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         uint32_t g = 0;
         bool ok = true;
         for (int r = 0, w; ok && (w = work_at(r, total_work)) >= 0; ++r) {
-          const Work wk = get_work<kCausal, kPacked, kVarlen>(P, w);
+          const Work wk = get_work<kCausal, kPacked>(P, w);
           for (int it = 0; ok && it < wk.n_max; ++it, ++g) {
             const int j = wk.n_max - 1 - it, s = g % kStages;
             if (!(ok = wait_bar<false>(bars + Bars::k_full + 8 * s, (g / kStages) & 1, abort_s, P.status, 40))) break;
@@ -561,7 +599,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         uint32_t sq[2] = {0, 0};              // QK groups issued so far per tile slot (= S_t tiles produced)
         uint32_t qn[2] = {0, 0};              // Q tiles taken so far per slot
         for (int r = 0, w; ok && (w = work_at(r, total_work)) >= 0; ++r) {
-          const Work wk = get_work<kCausal, kPacked, kVarlen>(P, w);
+          const Work wk = get_work<kCausal, kPacked>(P, w);
           for (int it = 0; ok && it < wk.n_max; ++it, ++g) {
             const int j = wk.n_max - 1 - it, s = g % kStages;
             const uint32_t ph = (g / kStages) & 1;
@@ -622,7 +660,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         bool ok = true;
         uint32_t g = 0, pv_cnt[2] = {0, 0}, pv_total = 0;
         for (int r = 0, w; ok && (w = work_at(r, total_work)) >= 0; ++r) {
-          const Work wk = get_work<kCausal, kPacked, kVarlen>(P, w);
+          const Work wk = get_work<kCausal, kPacked>(P, w);
           for (int it = 0; ok && it < wk.n_max; ++it, ++g) {
             const int j = wk.n_max - 1 - it, s = g % kStages;
             const bool act1 = j < wk.n_t[1];
@@ -677,18 +715,21 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       uint32_t g0 = 0;                                           // K/V stages the CTA used before this work item
       bool ok = true;
       for (int r = 0, w; ok && (w = work_at(r, total_work)) >= 0; ++r) {
-        const Work wk = get_work<kCausal, kPacked, kVarlen>(P, w);
+        const Work wk = get_work<kCausal, kPacked>(P, w);
         const int n_mine = wk.n_t[t];
         const uint32_t g_first = g0 + (uint32_t)(wk.n_max - n_mine);   // stage counter of this tile's first key tile
         g0 += (uint32_t)wk.n_max;
         const int qt = 2 * wk.pair + t;
         const int q0 = qt * kBlockM, qpos = q0 + row;
-        // (variable-length batches: the output is the packed [tokens, Hq, D] tensor)
-        __nv_bfloat16* orow = P.out + (kVarlen ? 0 : wk.b * P.o_sb) + wk.hq * P.o_sh + (int64_t)(wk.q_base + qpos) * P.o_sn;
+#if SAGE3_VARLEN_BUILD
+        __nv_bfloat16* orow = P.out + wk.hq * P.o_sh + (int64_t)(wk.q_base + qpos) * P.o_sn;   // packed output
+#else
+        __nv_bfloat16* orow = P.out + wk.b * P.o_sb + wk.hq * P.o_sh + (int64_t)qpos * P.o_sn;
+#endif
         if (n_mine == 0) {
           // query tile that sees no key at all (causal, more queries than keys): zeros, like the
           // reference's store_zero (fwd_epilogue.cu:150-183); nothing if the tile does not exist
-          if (qpos < wk.Nq) {
+          if (SEQ_TILE_EXISTS && qpos < SEQ_NQ) {
             for (int i = 0; i < D / 8; ++i) reinterpret_cast<uint4*>(orow)[i] = make_uint4(0, 0, 0, 0);
             if (P.lse) P.lse[((int64_t)wk.b * P.Hq + wk.hq) * P.Nq + qpos] = INFINITY;
           }
@@ -697,11 +738,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         // last visible key (slot): key padding, and the bottom-right aligned causal diagonal - in K-packing mode
         // the slots of the tokens up to the diagonal one
         auto causal_limit = [&](const int qp) {
-          const int tok = qp + wk.Nk_log - wk.Nq;                // last visible key token
+          const int tok = qp + SEQ_NK_LOG - SEQ_NQ;              // last visible key token
           if (!kPacked) return tok;
           return tok < 0 ? -1 : packed_slot_of_token(tok);
         };
-        const int key_lim = min(wk.Nk - 1, kCausal ? causal_limit(qpos) : 0x7fffffff);
+        const int key_lim = min(SEQ_NK - 1, kCausal ? causal_limit(qpos) : 0x7fffffff);
         const int first_row_lim = kCausal ? causal_limit(q0) : 0x7fffffff;
         float2 O2[D / 2];
 #pragma unroll
@@ -711,7 +752,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         for (int it = 0; it < n_mine; ++it, ++sc) {
           const int j = n_mine - 1 - it;
           const int n0 = j * kBlockN;
-          const bool need_mask = (n0 + kBlockN - 1 >= wk.Nk) || (kCausal && n0 + kBlockN - 1 > first_row_lim);
+          const bool need_mask = (n0 + kBlockN - 1 >= SEQ_NK) || (kCausal && n0 + kBlockN - 1 > first_row_lim);
           const float* lam_s = nullptr;
           if (kPacked) {
             // lambda of this key tile arrived with its K stage, i.e. before the Q.K^T MMA whose completion is
@@ -764,7 +805,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         }
 
         // ---- epilogue: O / l -> bf16 -> global (row-contiguous 16-byte stores)
-        if (ok && qpos < wk.Nq) {
+        if (ok && qpos < SEQ_NQ) {
           const float inv = (l == 0.f || l != l) ? 0.f : 1.0f / l;
 #pragma unroll
           for (int i = 0; i < D / 8; ++i) {
@@ -823,7 +864,7 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint32_t row_byte
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int D, bool kCausal, bool kPacked, bool kVarlen>
+template <int D, bool kCausal, bool kPacked>
 cudaError_t launch(const AttnArgs& a, cudaStream_t stream) {
   using L = Smem<D>;
   const int Tq = (a.Nq + 127) / 128, Tk = (a.Nk + 127) / 128;
@@ -842,8 +883,10 @@ cudaError_t launch(const AttnArgs& a, cudaStream_t stream) {
   P.lam = a.k_lambda;
   // K-packing mode: Nk counts key slots; 16 slots hold 15 tokens, a partial group one slot more than its tokens
   P.Nk_log = kPacked ? (a.Nk / 16) * 15 + (a.Nk % 16 == 0 ? 0 : a.Nk % 16 - 1) : a.Nk;
+#if SAGE3_VARLEN_BUILD
   P.cu_q = a.cu_q; P.cu_k = a.cu_k;
-  auto kern = attn_fwd_kernel<D, kCausal, kPacked, kVarlen>;
+#endif
+  auto kern = attn_fwd_kernel<D, kCausal, kPacked>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total + 1024);
   if (e != cudaSuccess) return e;
   // persistent CTAs: one per SM (registers and tensor memory allow exactly one), each walks the work list
@@ -858,21 +901,25 @@ cudaError_t launch(const AttnArgs& a, cudaStream_t stream) {
 
 }  // namespace
 
+#if SAGE3_VARLEN_BUILD
+cudaError_t launch_attn_fwd_varlen(const AttnArgs& a, cudaStream_t stream) {
+  // offsets come in pairs; no K-packing and no LSE for packed batches
+  if (a.cu_q == nullptr || a.cu_k == nullptr || a.k_lambda != nullptr || a.lse != nullptr) return cudaErrorInvalidValue;
+  if (a.D == 128) return a.causal ? launch<128, true, false>(a, stream) : launch<128, false, false>(a, stream);
+  if (a.D == 64) return a.causal ? launch<64, true, false>(a, stream) : launch<64, false, false>(a, stream);
+  return cudaErrorInvalidValue;
+}
+#else
 cudaError_t launch_attn_fwd(const AttnArgs& a, cudaStream_t stream) {
   if (a.D != 128 && a.D != 64) return cudaErrorInvalidValue;
-  const bool varlen = a.cu_q != nullptr || a.cu_k != nullptr;
-  if (varlen && (a.cu_q == nullptr || a.cu_k == nullptr || a.k_lambda != nullptr || a.lse != nullptr))
-    return cudaErrorInvalidValue;            // offsets come in pairs; no K-packing and no LSE for packed batches
   if (a.k_lambda) {
-    if (a.D == 128) return a.causal ? launch<128, true, true, false>(a, stream) : launch<128, false, true, false>(a, stream);
-    return a.causal ? launch<64, true, true, false>(a, stream) : launch<64, false, true, false>(a, stream);
+    if (a.D == 128) return a.causal ? launch<128, true, true>(a, stream) : launch<128, false, true>(a, stream);
+    return a.causal ? launch<64, true, true>(a, stream) : launch<64, false, true>(a, stream);
   }
-  if (varlen) {
-    if (a.D == 128) return a.causal ? launch<128, true, false, true>(a, stream) : launch<128, false, false, true>(a, stream);
-    return a.causal ? launch<64, true, false, true>(a, stream) : launch<64, false, false, true>(a, stream);
-  }
-  if (a.D == 128) return a.causal ? launch<128, true, false, false>(a, stream) : launch<128, false, false, false>(a, stream);
-  return a.causal ? launch<64, true, false, false>(a, stream) : launch<64, false, false, false>(a, stream);
+  if (a.D == 128) return a.causal ? launch<128, true, false>(a, stream) : launch<128, false, false>(a, stream);
+  return a.causal ? launch<64, true, false>(a, stream) : launch<64, false, false>(a, stream);
 }
+
+#endif
 
 }  // namespace sage3

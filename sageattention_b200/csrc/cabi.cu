@@ -175,7 +175,7 @@ static int attn_fwd_impl(const sage3_attn_args* a, const float* k_lambda, const 
   k.sm_scale = a->sm_scale; k.causal = a->is_causal;
   k.k_lambda = k_lambda;
   k.cu_q = cu_q; k.cu_k = cu_k;
-  e = sage3::launch_attn_fwd(k, stream);
+  e = (cu_q != nullptr || cu_k != nullptr) ? sage3::launch_attn_fwd_varlen(k, stream) : sage3::launch_attn_fwd(k, stream);
   if (e != cudaSuccess) return cuda_fail(e);
   return SAGE3_OK;
 }

@@ -67,5 +67,6 @@ struct AttnArgs {
   const int* cu_k = nullptr;
 };
 cudaError_t launch_attn_fwd(const AttnArgs& a, cudaStream_t stream);
+cudaError_t launch_attn_fwd_varlen(const AttnArgs& a, cudaStream_t stream);   // cu_q / cu_k given
 
 }  // namespace sage3
