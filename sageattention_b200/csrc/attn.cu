@@ -110,7 +110,10 @@ struct Smem {
                                                           // stages because the softmax reads it after the stage is freed
   static constexpr int stats = lam + 2 * kStages * 512;   // [2][8 blocks][128 rows] float2 (exponent offset, scale)
   static constexpr int bars = stats + 2 * 8 * 128 * 8;
-  static constexpr int total = bars + 512;
+  // output staging for the TMA store: [2 tiles][D/64 column halves][128 rows x 128 bytes], 128-byte swizzle
+  static constexpr int kOStage = 128 * 128;
+  static constexpr int ostage = (bars + 512 + 1023) / 1024 * 1024;
+  static constexpr int total = ostage + ((!SAGE3_VARLEN_BUILD && D == 128) ? 2 * (D / 64) * kOStage : 0);
 };
 
 struct Bars {            // byte offsets inside the barrier block
@@ -127,7 +130,8 @@ struct Bars {            // byte offsets inside the barrier block
   static constexpr int o_free = o_full + 16;
   static constexpr int drain = o_free + 8;                // [2] the issuers' last commit when giving up
   static constexpr int p_half = drain + 16;               // [2] first 64 keys of P^ (and their scales) written
-  static constexpr int tmem_slot = p_half + 16;             // u32 written by tcgen05.alloc
+  static constexpr int epi = p_half + 16;                 // [2] rendezvous of a softmax warpgroup around its output staging
+  static constexpr int tmem_slot = epi + 16;             // u32 written by tcgen05.alloc
   static constexpr int abort_flag = tmem_slot + 8;
   static constexpr int run_flag = abort_flag + 4;
 };
@@ -143,6 +147,7 @@ struct KParams {
   float scale_log2;      // sm_scale * log2(e)
   const float* lam;      // K-packing mode: lambda per key slot, fp32 [B,Hkv,Tk*128]; Nk is the packed length
   int Nk_log;            // number of key tokens (= Nk unless packed)
+  bool o_token_first;    // output tensor map: coordinates (d, token, head, batch) or (d, head, token, batch)
 #if SAGE3_VARLEN_BUILD
   const int *cu_q, *cu_k; // token offsets of the sequences (device int32 [B+1]); Nq, Nk, Tq, Tk then describe the
                           // LONGEST sequence, i.e. the rectangular operand layouts
@@ -428,11 +433,13 @@ template <int D, bool kCausal, bool kPacked>
 __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,
                                                                    const __grid_constant__ CUtensorMap tm_k,
                                                                    const __grid_constant__ CUtensorMap tm_v,
+                                                                   const __grid_constant__ CUtensorMap tm_o,
                                                                    const KParams P) {
   using L = Smem<D>;
   constexpr int kKB = D / 64;                              // K=64 blocks of the QK contraction
   constexpr uint32_t kSwzQK = (D == 128) ? 4u : 6u;        // 64-byte / 32-byte swizzle
   constexpr uint32_t kSboQK = (D == 128) ? 512u : 256u;
+  constexpr bool kTmaStore = !SAGE3_VARLEN_BUILD && D == 128;   // see the epilogue
   constexpr bool kIssuerHint = (D == 64);                  // the MMA issuers of the D=64 kernel do better with the longer park
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // swizzled tiles need 1024-byte alignment
@@ -450,6 +457,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       mbar_init(bars + Bars::s_full + 8 * t, 1);
       mbar_init(bars + Bars::p_full + 8 * t, 128);
       mbar_init(bars + Bars::p_half + 8 * t, 128);
+      mbar_init(bars + Bars::epi + 8 * t, 128);
       mbar_init(bars + Bars::o_full + 8 * t, 1);
     }
     for (int s = 0; s < kStages; ++s) {
@@ -498,7 +506,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(RegSplit<D>::role));
       if (warp == 8 && lane == 0) {
         // ---------------------------------------------------------------- TMA producer
-        prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
+        prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_o);
         uint32_t g = 0;                       // K/V stages completely issued so far
         uint32_t gk = 0;                      // K stages issued so far (g or g + 1)
         uint32_t qn[2] = {0, 0};              // Q tiles loaded so far per slot
@@ -712,6 +720,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       const uint32_t bar_s = bars + Bars::s_full + 8 * t, bar_p = bars + Bars::p_full + 8 * t;
       const uint32_t bar_o = bars + Bars::o_full + 8 * t, bar_h = bars + Bars::p_half + 8 * t;
       uint32_t sc = 0;                                           // key tiles processed so far by this warpgroup
+      uint32_t ne = 0;                                           // epilogue rendezvous so far
       uint32_t g0 = 0;                                           // K/V stages the CTA used before this work item
       bool ok = true;
       for (int r = 0, w; ok && (w = work_at(r, total_work)) >= 0; ++r) {
@@ -804,8 +813,42 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           }
         }
 
-        // ---- epilogue: O / l -> bf16 -> global (row-contiguous 16-byte stores)
-        if (ok && qpos < SEQ_NQ) {
+        // ---- epilogue: O / l -> bf16 -> global.  D=128, dense batches: through a swizzled staging tile in shared
+        // memory and one TMA store per 64 columns - a thread owns a whole output row, so direct stores put 32
+        // different rows into every store instruction; at N = 1K that cost 6 400 cycles per work item and
+        // warpgroup, one and a half key tiles.  D=64 (half the bytes; measured 4 % slower with the staging) and
+        // packed variable-length outputs (a tile must not spill into the next sequence) store directly.
+        if (!ok) break;
+        if (kTmaStore) {
+          uint8_t* stage = smem + L::ostage + t * (D / 64) * L::kOStage;
+          const uint32_t bar_e = bars + Bars::epi + 8 * t;
+          // the stores of the previous work item must have left the staging tile
+          if (row == 0) bulk_wait_read0();
+          mbar_arrive(bar_e);
+          if (!(ok = wait_bar<false>(bar_e, ne & 1, abort_s, P.status, 35))) break;
+          ++ne;
+          const float inv = (l == 0.f || l != l) ? 0.f : 1.0f / l;
+#pragma unroll
+          for (int i = 0; i < D / 8; ++i) {
+            uint4 o;
+            o.x = pack_bf16(O2[4 * i + 0].x * inv, O2[4 * i + 0].y * inv);
+            o.y = pack_bf16(O2[4 * i + 1].x * inv, O2[4 * i + 1].y * inv);
+            o.z = pack_bf16(O2[4 * i + 2].x * inv, O2[4 * i + 2].y * inv);
+            o.w = pack_bf16(O2[4 * i + 3].x * inv, O2[4 * i + 3].y * inv);
+            *reinterpret_cast<uint4*>(stage + (i >> 3) * L::kOStage + row * 128 + (((i & 7) ^ (row & 7)) << 4)) = o;
+          }
+          fence_proxy_async_smem();
+          mbar_arrive(bar_e);
+          if (!(ok = wait_bar<false>(bar_e, ne & 1, abort_s, P.status, 36))) break;
+          ++ne;
+          if (row == 0) {
+#pragma unroll
+            for (int hcol = 0; hcol < D / 64; ++hcol)
+              tma_store_4d(&tm_o, sbase + L::ostage + (t * (D / 64) + hcol) * L::kOStage, 64 * hcol,
+                           P.o_token_first ? q0 : wk.hq, P.o_token_first ? wk.hq : q0, wk.b);
+            bulk_commit_group();
+          }
+        } else if (qpos < SEQ_NQ) {
           const float inv = (l == 0.f || l != l) ? 0.f : 1.0f / l;
 #pragma unroll
           for (int i = 0; i < D / 8; ++i) {
@@ -816,6 +859,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
             o.w = pack_bf16(O2[4 * i + 3].x * inv, O2[4 * i + 3].y * inv);
             reinterpret_cast<uint4*>(orow)[i] = o;
           }
+        }
+        if (qpos < SEQ_NQ) {
           if (P.lse) {
             // natural-log sum of exp(sm_scale * s) over the row (l carries the factor 2688)
             P.lse[((int64_t)wk.b * P.Hq + wk.hq) * P.Nq + qpos] =
@@ -823,6 +868,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           }
         }
       }
+      if (kTmaStore && row == 0) bulk_wait_read0();   // the last output tiles have left shared memory before the CTA ends
     }
   }
 
@@ -864,6 +910,36 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint32_t row_byte
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// bf16 output [B][Hq][Nq][D] with arbitrary element strides, box = 128 rows x 64 columns (128 bytes, swizzled).
+// Tensor-map strides must grow with the dimension, so tokens and heads are ordered by their stride ("HND": D, N,
+// H, B; "NHD": D, H, N, B); *n_dim tells the kernel which coordinate is the token.
+bool make_out_map(CUtensorMap* m, const void* base, int B, int H, int N, int D, int64_t sb, int64_t sh, int64_t sn,
+                  int* n_dim) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return false;
+  // a dimension of extent 1 never advances; give it a stride that keeps the order valid
+  const bool n_first = (H == 1) || (N > 1 && sn <= sh);
+  *n_dim = n_first ? 1 : 2;
+  cuuint64_t dims[4] = {(cuuint64_t)D, 0, 0, (cuuint64_t)B};
+  cuuint64_t strides[3];
+  cuuint32_t box[4] = {64, 1, 1, 1};
+  const cuuint64_t s_n = (cuuint64_t)sn * 2, s_h = (cuuint64_t)sh * 2;
+  if (n_first) {
+    dims[1] = N; dims[2] = H; box[1] = 128;
+    strides[0] = N > 1 ? s_n : (cuuint64_t)D * 2;
+    strides[1] = H > 1 ? s_h : strides[0] * N;
+  } else {
+    dims[1] = H; dims[2] = N; box[2] = 128;
+    strides[0] = s_h;
+    strides[1] = N > 1 ? s_n : strides[0] * H;
+  }
+  strides[2] = B > 1 ? (cuuint64_t)sb * 2 : strides[1] * dims[2];
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int D, bool kCausal, bool kPacked>
 cudaError_t launch(const AttnArgs& a, cudaStream_t stream) {
   using L = Smem<D>;
@@ -874,12 +950,18 @@ cudaError_t launch(const AttnArgs& a, cudaStream_t stream) {
   if (!make_map(&tk, a.k_codes, (uint64_t)a.B * a.Hkv * Tk * 128, D / 2, 128, swz)) return cudaErrorInvalidValue;
   if (!make_map(&tv, a.vt_codes, (uint64_t)a.B * a.Hkv * Tk * D, 64, D, CU_TENSOR_MAP_SWIZZLE_64B))
     return cudaErrorInvalidValue;
+  CUtensorMap to = tq;                       // only D=128 dense batches store through it
+  int o_ndim = 1;
+  if (!SAGE3_VARLEN_BUILD && D == 128 &&
+      !make_out_map(&to, a.out, a.B, a.Hq, a.Nq, D, a.o_sb, a.o_sh, a.o_sn, &o_ndim))
+    return cudaErrorInvalidValue;
   KParams P;
   P.q_sf = (const uint8_t*)a.q_sf; P.k_sf = (const uint8_t*)a.k_sf; P.vt_sf = (const uint8_t*)a.vt_sf;
   P.ds = (const __nv_bfloat16*)a.ds; P.out = (__nv_bfloat16*)a.out; P.lse = a.lse; P.status = a.status;
   P.o_sb = a.o_sb; P.o_sh = a.o_sh; P.o_sn = a.o_sn;
   P.B = a.B; P.Hq = a.Hq; P.Hkv = a.Hkv; P.Nq = a.Nq; P.Nk = a.Nk; P.Tq = Tq; P.Tk = Tk; P.ds_rows = a.ds_rows;
   P.scale_log2 = a.sm_scale * kLog2e;
+  P.o_token_first = o_ndim == 1;
   P.lam = a.k_lambda;
   // K-packing mode: Nk counts key slots; 16 slots hold 15 tokens, a partial group one slot more than its tokens
   P.Nk_log = kPacked ? (a.Nk / 16) * 15 + (a.Nk % 16 == 0 ? 0 : a.Nk % 16 - 1) : a.Nk;
@@ -895,7 +977,7 @@ cudaError_t launch(const AttnArgs& a, cudaStream_t stream) {
   if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
   const int64_t work = (int64_t)a.B * a.Hq * ((Tq + 1) / 2);
   const int64_t grid = work < sms ? work : sms;
-  kern<<<(unsigned)grid, kAttnThreads, L::total + 1024, stream>>>(tq, tk, tv, P);
+  kern<<<(unsigned)grid, kAttnThreads, L::total + 1024, stream>>>(tq, tk, tv, to, P);
   return cudaGetLastError();
 }
 
