@@ -13,14 +13,16 @@
 //   O /= l, bf16                                      softmax_fused.h:156-173, fwd_epilogue.cu:103-147
 // Key tiles are visited from the last to the first as the reference does (fwd_mainloop.cu:575).
 //
-// One persistent CTA per SM walks a static list of work items (CTA i takes items i, i + grid, ...);
+// One persistent CTA per SM walks a static list of work items (round r: item r*grid + i, odd rounds in
+// reverse CTA order; causal items sorted by falling cost over all heads);
 // an item is TWO adjacent 128-row query tiles of one head, which share every K / V tile.  All
 // barrier phases keep counting across items, so the loads and the first Q.K^T of the next item are
 // under way while the last softmax, fold and output store of the current one finish.  12 warps:
 //   warps 0-3   softmax warpgroup of query tile 0: thread r owns score row r (tensor-memory lane r)
 //               and the O row in registers.  Per key tile: pass 1 scans S for the 16-key block
 //               maxima, pass 2 turns S into P^; every tensor-memory load is issued one block ahead
-//               of its use; then the P.V product is folded into O.
+//               of its use; then the P.V product is folded into O.  At the end of an item O / l goes
+//               out as bf16 (D=128: through a swizzled staging tile and TMA stores).
 //   warps 4-7   the same for query tile 1; the two warpgroups run half a period apart, so one does
 //               softmax arithmetic while the other waits for its MMAs
 //   warp  8     TMA producer (Q tiles per item, then a ring of K and V stages; scale factors and the
