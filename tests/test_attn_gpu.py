@@ -205,3 +205,20 @@ def test_custom_op_runs_and_matches_direct_call():
         assert torch.equal(direct, via_op)
     torch.library.opcheck(compile_ops.fp4_attention_op, (q, k, v, "HND", False, 0.0, True, False),
                           test_utils=("test_schema", "test_faketensor"))
+
+
+def test_operator_can_be_captured_in_a_cuda_graph():
+    """The whole operator (memsets + four kernels, no allocation or synchronisation inside the library) is
+    captured once and replayed on new input values."""
+    q, k, v = U.make_qkv(2, 4, 2, 700, 700, 128, seed=21, device=DEV)
+    for _ in range(2):
+        sa.sageattn(q, k, v, is_causal=True)                   # warm up (lazy driver look-ups, allocator)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        out = sa.sageattn(q, k, v, is_causal=True)
+    q2, k2, v2 = U.make_qkv(2, 4, 2, 700, 700, 128, seed=22, device=DEV)
+    q.copy_(q2); k.copy_(k2); v.copy_(v2)
+    g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, sa.sageattn(q2, k2, v2, is_causal=True))
