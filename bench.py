@@ -17,6 +17,12 @@ reference's video-model activations):
            by their log-sum-exp (needs N>1)
 With N GPUs the `dit` / `prefill` workloads are sharded over batch x heads with no collective: every
 rank processes the same per-GPU workload (weak scaling) and the value is the sum over ranks.
+
+Every default run also carries a `"ulysses"` object: the long-sequence configuration (B=1 H=40 N=75600 D=128,
+the one multi-GPU path that communicates) in strong scaling - at N=1 the plain operator on the whole problem, at
+N>1 `ulysses_attention` on sequence-sharded inputs (all-to-all over NCCL), after a parity check on a reduced
+shape against the single-GPU operator; rank 0 also times the whole problem on its own GPU so that the line
+carries `efficiency = t_1 / (N * t_N)` measured in the same run.
 """
 from __future__ import annotations
 
@@ -43,6 +49,10 @@ WORKLOADS = {
     "profile": dict(B=1, Hq=10, Hkv=10, N=32760, D=128, causal=False, k_off=2.0, v_out=0.05),   # a quarter of dit
     "small": dict(B=1, Hq=8, Hkv=8, N=1024, D=128, causal=False, k_off=2.0, v_out=0.0),
 }
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one attention launch, per head, at N = 32760, D = 128 (ncu)
+TRAFFIC_PER_HEAD_DIT = 30.05e6
 
 
 def attn_flops(B, Hq, Nq, Nk, D, causal):
@@ -211,6 +221,178 @@ def run_sweep(args):
 
 
 # --------------------------------------------------------------------------------------------------
+# the reference's own quantisation kernels on the same tensors (oracle/_ref, built by oracle/build_ref.py)
+# --------------------------------------------------------------------------------------------------
+
+def time_reference_quant(q, k, v, reps=3):
+    """Milliseconds of the reference preprocessing on this GPU: eager K smoothing + padding, its Triton-free parts
+    of the Q block mean done in eager PyTorch, delta_s GEMM, and its three CUDA quantisation kernels
+    (quantization/fp4_quantization_4d.cu: scaled_fp4_quant, _permute, _trans), timed with CUDA events outside
+    the bench's timed region.  Returns None when the checker library is not built."""
+    import importlib.util
+    so = ROOT / "oracle" / "_ref" / "sage_ref_quant_cuda.so"
+    if not so.exists():
+        return None
+    spec = importlib.util.spec_from_file_location("sage_ref_quant_cuda", so)
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    B, H, N, D = q.shape
+    Hk = k.shape[1]
+    Np = (N + 127) // 128 * 128
+    dev = q.device
+    pad = lambda x: torch.nn.functional.pad(x, (0, 0, 0, Np - N)) if Np != N else x
+
+    def kernels_only(qs, ks, vp, bufs):
+        ref.scaled_fp4_quant(qs, bufs[0], bufs[1], 1)
+        ref.scaled_fp4_quant_permute(ks, bufs[2], bufs[3], 1)
+        ref.scaled_fp4_quant_trans(vp, bufs[4], bufs[5], 1)
+
+    def whole(bufs):
+        ks = pad(k - k.mean(dim=-2, keepdim=True))                                  # api.py:184, 196-203
+        qp = pad(q)
+        g = qp.float().reshape(B, H, Np // 128, 128, D)
+        qm = g.mean(dim=-2)
+        qs = (g - qm.unsqueeze(-2)).to(torch.bfloat16).reshape(B, H, Np, D)         # api.py:26-72 (Triton there)
+        kr = ks if H == Hk else ks.repeat_interleave(H // Hk, dim=1)
+        ds = torch.matmul(qm.to(torch.bfloat16), kr.transpose(-2, -1)).float()      # api.py:201
+        kernels_only(qs, ks, pad(v), bufs)
+        return qs, ks, ds
+
+    u8 = dict(dtype=torch.uint8, device=dev)
+    f8 = dict(dtype=torch.float8_e4m3fn, device=dev)
+    bufs = [torch.empty((B, H, Np, D // 2), **u8), torch.empty((B, H, Np, D // 16), **f8),
+            torch.empty((B, Hk, Np, D // 2), **u8), torch.empty((B, Hk, Np, D // 16), **f8),
+            torch.empty((B, Hk, D, Np // 2), **u8), torch.empty((B, Hk, D, Np // 16), **f8)]
+    qs, ks, _ = whole(bufs)
+    vp = pad(v)
+    out = {}
+    for name, fn in (("kernels_ms", lambda: kernels_only(qs, ks, vp, bufs)), ("pipeline_ms", lambda: whole(bufs))):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        out[name] = e0.elapsed_time(e1) / reps
+    return out
+
+
+# --------------------------------------------------------------------------------------------------
+# the long-sequence configuration (Ulysses all-to-all), part of every default run
+# --------------------------------------------------------------------------------------------------
+
+def _ulysses_parity(sa, sd, dist, dev, world, rank):
+    """Reduced shape, every rank: the Ulysses output shard must be BITWISE the single-GPU operator's output for the
+    same tokens when that operator is given the gathered full sequence of exactly the heads each Ulysses call
+    attends (the K channel means are fp32 sums whose chunking depends on the number of heads in a call).  The ring
+    scheme quantises every K/V shard on its own, so it is compared within a tolerance and against fp32 SDPA."""
+    from oracle import sage3
+    B, n, D = 1, 333, 128
+    sizes = [1, 2]
+    H = world * sum(sizes)
+    g = torch.Generator(device=dev).manual_seed(77 + rank)
+    q, k, v = (torch.randn((B, n, H, D), generator=g, device=dev).to(torch.bfloat16) for _ in range(3))
+    k = (k.float() + 1.5).to(torch.bfloat16)
+    full = []
+    for t in (q, k, v):
+        parts = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(parts, t.contiguous())
+        full.append(torch.cat(parts, dim=1))                        # [B, N, H, D]
+    got = sd.ulysses_attention(q, k, v, head_chunks=sizes)
+    want = torch.empty_like(full[0])
+    start = 0
+    for n_c in sizes:
+        for p in range(world):
+            sl = slice(start + p * n_c, start + (p + 1) * n_c)
+            want[:, :, sl] = sa.sageattn(full[0][:, :, sl].contiguous(), full[1][:, :, sl].contiguous(),
+                                         full[2][:, :, sl].contiguous(), tensor_layout="NHD")
+        start += world * n_c
+    mine = slice(rank * n, (rank + 1) * n)
+    bitwise = bool(torch.equal(got, want[:, mine]))
+    ring = sd.ring_attention(q, k, v)
+    ref = sage3.sdpa_fp32(*(t.cpu().transpose(1, 2) for t in full)).transpose(1, 2)[:, mine]
+    cos_ring, l1_ring = sage3.accuracy(ring.float().cpu(), ref)
+    cos_one, l1_one = sage3.accuracy(want[:, mine].float().cpu(), ref)
+    flags = torch.tensor([int(bitwise), int(cos_ring >= cos_one - 5e-3)], device=dev)
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    return {"ulysses_parity": "bitwise" if int(flags[0]) else "MISMATCH",
+            "ring_parity": {"ok": bool(int(flags[1])), "cos_vs_fp32_sdpa": cos_ring, "single_gpu_cos_vs_fp32_sdpa": cos_one,
+                            "tolerance": "cosine vs fp32 SDPA no more than 5e-3 below the single-GPU operator's"},
+            "parity_shape": {"B": B, "H": H, "N": n * world, "D": D, "head_chunks": sizes}}
+
+
+def run_ulysses_leg(sa, dist, dev, world, rank, steps):
+    w = WORKLOADS["ulysses"]
+    B, H, N, D = w["B"], w["Hq"], w["N"], w["D"]
+    flops = attn_flops(B, H, N, N, D, False)
+    out = {"config": {"workload": "ulysses", "B": B, "H": H, "N": N, "D": D, "causal": False}, "n_gpus": world,
+           "scaling": "strong", "steps": steps, "warmup": 3}
+
+    def time_single():
+        q, k, v = gen_inputs(w, seed=4321, device=dev)
+        for _ in range(3):
+            sa.sageattn(q, k, v)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            sa.sageattn(q, k, v)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    if world == 1:
+        ms = time_single()
+        out.update(ms_per_step=ms, tops=flops / (ms * 1e-3) / 1e12, single_gpu_ms=ms, efficiency=1.0,
+                   step="the plain operator on the whole problem (nothing to exchange on one GPU)")
+        return out
+    from sageattention_b200 import distributed as sd
+    if N % world or H % world:
+        out["skipped"] = f"{world} GPUs divide neither {H} heads nor {N} tokens"
+        return out
+    out.update(_ulysses_parity(sa, sd, dist, dev, world, rank))
+    n, hpr = N // world, H // world
+    g = torch.Generator(device=dev).manual_seed(4321 + rank)
+    q = torch.randn((B, n, H, D), generator=g, device=dev).to(torch.bfloat16)
+    koff = torch.randn((B, 1, H, D), generator=torch.Generator(device=dev).manual_seed(99), device=dev) * w["k_off"]
+    k = (torch.randn((B, n, H, D), generator=g, device=dev) + koff).to(torch.bfloat16)
+    v = torch.randn((B, n, H, D), generator=g, device=dev).to(torch.bfloat16)
+    # heads per rank in chunks of about a fifth, the first and the last chunk the smallest: only the first exchange
+    # and the last return are exposed
+    per = max(1, hpr // 5)
+    sizes = [per] * (hpr // per)
+    if hpr % per:
+        sizes.insert(len(sizes) // 2, hpr % per)
+    for _ in range(3):
+        sd.ulysses_attention(q, k, v, head_chunks=sizes)
+    torch.cuda.synchronize()
+    dist.barrier()
+    exposed = []
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        sd.ulysses_attention(q, k, v, head_chunks=sizes, exposed=exposed)
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    t = torch.tensor([e0.elapsed_time(e1) / steps, sum(a.elapsed_time(b) for a, b in exposed) / steps],
+                     device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, exp_ms = t.tolist()
+    del q, k, v
+    torch.cuda.empty_cache()
+    single = time_single() if rank == 0 else 0.0
+    dist.barrier()
+    out.update(ms_per_step=ms, tops=flops / (ms * 1e-3) / 1e12, exposed_all_to_all_ms=exp_ms, single_gpu_ms=single,
+               efficiency=(single / (world * ms)) if single else None, head_chunks=sizes,
+               step=f"3 all-to-all in + operator + 1 all-to-all out per head chunk, {hpr} heads per GPU; "
+                    "exposed = time the compute stream waited for a collective (max over ranks)")
+    return out
+
+
+# --------------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------------
 
@@ -317,37 +499,94 @@ def main():
     h2d = sum(x.numel() * 2 for x in (qh, kh, vh))
     d2h = oh.numel() * 2
 
+    # what the copies alone take on this rank (all ranks copy at the same time, as in the e2e step): pinned host ->
+    # device of Q, K, V and device -> host of the output, each on its own, then the e2e step is compared with the
+    # slower of the two (they run in opposite directions and overlap)
+    def copy_ms(fn):
+        fn()
+        torch.cuda.synchronize()
+        if dist:
+            dist.barrier()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        for _ in range(3):
+            fn()
+        c1.record()
+        torch.cuda.synchronize()
+        return c0.elapsed_time(c1) / 3
+    o_dev = torch.empty_like(q)
+    h2d_ms = copy_ms(lambda: [d.copy_(h, non_blocking=True) for d, h in ((q, qh), (k, kh), (v, vh))])
+    d2h_ms = copy_ms(lambda: oh.copy_(o_dev, non_blocking=True))
+    cm = torch.tensor([h2d_ms, d2h_ms], device=dev, dtype=torch.float64)
+    if dist:
+        dist.all_reduce(cm, op=dist.ReduceOp.MAX)
+    h2d_ms, d2h_ms = cm.tolist()
+    del o_dev
+
+    ref_quant = time_reference_quant(q, k, v) if rank == 0 else None
+    peak_tf, peak_note = None, None
+    if rank == 0:
+        import ctypes as C
+        lib = sa._lib.load()
+        st = torch.zeros(1, dtype=torch.int32, device=dev)
+        best = 0.0
+        for n_cols in (128, 256):
+            val = C.c_double()
+            rc = lib.sage3_fp4_mma_peak(n_cols, 256, 8, st.data_ptr(), torch.cuda.current_stream().cuda_stream, C.byref(val))
+            if rc == 0 and val.value > best:
+                best, peak_note = val.value, f"M=128 N={n_cols} K=64"
+        peak_tf = best if best > 0 else None
+    del qh, kh, vh, oh, q, k, v
+    torch.cuda.empty_cache()
+    uly = run_ulysses_leg(sa, dist, dev, world, rank, steps=3) if args.workload == "dit" else None
+
     if rank != 0:
         if dist:
             dist.destroy_process_group()
         return
     hbm, bf16_burst, bf16_sus, which = measured_peaks()
-    peak_fp4 = 4.0 * bf16_sus          # dense FP4 : dense bf16 = 9 : 2.25 nominal; bf16 figure is the sustained one
+    # tensor roofline: the dense block-scaled FP4 MMA rate measured on this GPU a moment ago (back-to-back
+    # tcgen05.mma kind::mxf4nvf4 on resident operands, one CTA per SM); 4 x the cuBLAS bf16 figure only if that failed
+    peak_fp4 = peak_tf if peak_tf else 4.0 * bf16_sus
     achieved = flops / (attn_ms * 1e-3) / 1e12
     Tq = (N + 127) // 128
-    quant_bytes = B * N * ((Hq + 2 * Hkv) * (2 * D + D // 2 + D // 16)) + B * Hkv * N * 2 * D   # + second K read
+    quant_bytes = B * N * ((Hq + 2 * Hkv) * (2 * D + D // 2 + D // 16))          # one read of Q, K, V + codes + scales
     line = {
         "metric": "attention_tops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "fp4 (e2m1 x ue4m3 block-scaled, fp32 accumulate)", "data": "synthetic",
         "config": {"workload": args.workload, "B": B, "Hq": Hq, "Hkv": Hkv, "N": N, "D": D, "causal": causal,
                    "sharding": f"batch x heads over {world} GPU(s), no collective",
-                   "l2": "inputs (3 x %.0f MB bf16) exceed the 126 MB L2" % (q.numel() * 2 / 1e6),
+                   "l2": "inputs (3 x %.0f MB bf16) exceed the 126 MB L2" % (B * Hq * N * D * 2 / 1e6),
                    "step": "K mean + fused quant + delta_s + attention, inputs resident in HBM"},
         "kernel_only": {"attention_ms": attn_ms, "attention_tops": achieved, "preprocess_ms": quant_ms,
-                        "preprocess_gbs": quant_bytes / (quant_ms * 1e-3) / 1e9},
+                        "preprocess_gbs": quant_bytes / (quant_ms * 1e-3) / 1e9,
+                        "preprocess_frac_of_hbm": quant_bytes / (quant_ms * 1e-3) / 1e9 / hbm,
+                        "reference_quant": (None if ref_quant is None else {
+                            **ref_quant, "vs_reference_quant": ref_quant["pipeline_ms"] / quant_ms,
+                            "what": "the reference's preprocessing on the same tensors and GPU: pipeline_ms = eager "
+                                    "smoothing, block means, delta_s GEMM and its three CUDA quantisation kernels; "
+                                    "kernels_ms = those three kernels alone; ratio = pipeline_ms / preprocess_ms"})},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_fp4, "unit": "TFLOP/s",
                      "frac": achieved / peak_fp4,
-                     # ncu, quarter-size capture (profiles/attn_fwd_kernel_quarter_dit.md): 30.05 MB of DRAM traffic per
-                     # head at N = 32760, D = 128, proportional to the number of heads
-                     "traffic": (B * Hq * 30.05e6) if (N == 32760 and D == 128 and not causal) else None,
-                     "note": f"peak = 4 x {which} sustained bf16 cuBLAS ({bf16_sus} TF/s): dense FP4 is 4x dense bf16 on "
-                             f"B200; vs bf16 sustained itself: {achieved / bf16_sus:.3f}"},
+                     # DRAM bytes per launch from the ncu capture of a quarter of this workload, proportional to the
+                     # number of heads
+                     "traffic": (B * Hq * TRAFFIC_PER_HEAD_DIT) if (N == 32760 and D == 128 and not causal) else None,
+                     "note": (f"peak = dense FP4 MMA rate measured live on this GPU ({peak_note}, sage3_fp4_mma_peak)"
+                              if peak_tf else f"peak = 4 x {which} sustained bf16 cuBLAS (FP4 MMA measurement failed)")
+                             + f"; for context 4 x {which} sustained bf16 cuBLAS = {4 * bf16_sus:.0f}, "
+                               f"achieved / bf16 sustained = {achieved / bf16_sus:.3f}"},
         "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms.item()},
+                "ms_per_step": e2e_ms.item(),
+                "h2d_gbs_per_rank": h2d / (h2d_ms * 1e-3) / 1e9, "d2h_gbs_per_rank": d2h / (d2h_ms * 1e-3) / 1e9,
+                "copy_bound_ms": max(h2d_ms, d2h_ms),
+                "note": "copy rates measured with all ranks copying at once; the step cannot be shorter than the slower "
+                        "direction (copy_bound_ms) nor than the operator (ms_per_step of the line)"},
         "gpu_launches": 4 * args.steps,
         "clocks": clocks,
     }
+    if uly is not None:
+        line["ulysses"] = uly
     if not args.no_cpu_baseline:
         tops, dt, threads, sample = cpu_sample(w, rows=2048)
         line["cpu_baseline"] = {"value": tops, "unit": "TFLOP/s", "cores": threads, "kind": "port",

@@ -144,6 +144,9 @@ typedef struct {
                                 and padding                                                          */
   void* scratch;             /* as in sage3_quant_args (only used when the means are computed here)  */
   size_t scratch_bytes;
+  int32_t split_first;       /* V layout: 0 = a zero row in every mean slot; 1 = the reference's v_trick
+                                (api.py:158-170): slot 1 holds the group's first V row as the V^T quantiser
+                                rounds it, slot 0 the remainder                                        */
 } sage3_pack_args;
 
 /* Variable-length batch (the calling convention of sageattn_varlen, sageattention/core.py:334-358): packed
@@ -185,11 +188,15 @@ SAGE3_API int sage3_attention_varlen(const sage3_varlen_args* args, void* stream
  * 184, 193-194 (eager PyTorch in the reference); its outputs go through sage3_quant_qkv with
  * shape.Nk = sage3_packed_rows(Nk) and smooth_k = 0.  sage3_attn_fwd_packed is sage3_attn_fwd with the
  * lambda correction, slot masking and packed causal mask of fwd_mainloop.cu:273-324, 796-891 (per-block-mean
- * variant); args->shape.Nk must be sage3_packed_len(Nk), the number of occupied key slots (api.py:267-274). */
+ * variant when mean_slot_first == 0: the mean slot is masked out; the other variant, fwd_mainloop.cu:847-891,
+ * when mean_slot_first == 1: the slot takes the score of the group's first token and stays out of the row sum -
+ * to be used with split_first V and, as the reference pairs them, a whole-sequence Q mean, delta_s_rows == 1);
+ * args->shape.Nk must be sage3_packed_len(Nk), the number of occupied key slots (api.py:267-274). */
 SAGE3_API int sage3_packed_rows(int nk);   /* 16 * ceil(nk / 15): rows of the packed tensors                */
 SAGE3_API int sage3_packed_len(int nk);    /* occupied slots: 16 per full group, tokens + 1 for a partial one */
 SAGE3_API int sage3_pack_kv(const sage3_pack_args* args, void* stream);
-SAGE3_API int sage3_attn_fwd_packed(const sage3_attn_args* args, const float* k_lambda, void* stream);
+SAGE3_API int sage3_attn_fwd_packed(const sage3_attn_args* args, const float* k_lambda, int32_t mean_slot_first,
+                                    void* stream);
 
 /* K channel means (bf16 [B,Hkv,D] into km_out; shape->Hq and shape->Nq are ignored) for callers that
  * cannot allocate device memory where they run - for example a server that gave all device memory to
@@ -212,6 +219,21 @@ SAGE3_API int sage3_k_mean_static(const sage3_shape* shape, const sage3_tensor* 
 /* Synchronises `stream`, copies the device status word back and maps it to a status
  * (SAGE3_OK or SAGE3_ERR_DEVICE_WAIT); *code_out, if given, receives the raw word. */
 SAGE3_API int sage3_read_device_status(const int32_t* device_status, void* stream, int32_t* code_out);
+
+/* Self-test of the kernels' bounded waits: enqueues a one-CTA kernel that waits, with a short poll limit (a few
+ * milliseconds), on a barrier nothing completes.  The kernel returns normally and leaves code 77 in
+ * *device_status, so a following sage3_read_device_status reports SAGE3_ERR_DEVICE_WAIT; the context stays
+ * usable.  No counterpart in the reference. */
+SAGE3_API int sage3_selftest_bounded_wait(int32_t* device_status, void* stream);
+
+/* Measures the block-scaled FP4 tensor-core ceiling of the current GPU: one CTA per SM issues
+ * tcgen05.mma kind::mxf4nvf4 (M = 128, N = n_cols in {128, 256}, K = 64) back to back on operands resident in
+ * shared / tensor memory, `bursts` x 64 MMAs per launch, `launches` launches timed with CUDA events after one
+ * warm-up launch.  *tflops_out receives the dense rate (2*M*N*K flops per MMA).  Synchronises `stream`.
+ * No counterpart in the reference (its reports quote a data-sheet peak); the number is the denominator of the
+ * attention kernel's tensor roofline. */
+SAGE3_API int sage3_fp4_mma_peak(int n_cols, int bursts, int launches, int32_t* device_status, void* stream,
+                                 double* tflops_out);
 
 #ifdef __cplusplus
 }

@@ -117,7 +117,8 @@ def _e2m1_round(x: torch.Tensor) -> torch.Tensor:
 
 def attention_quantised(qd: torch.Tensor, kd: torch.Tensor, vtd: torch.Tensor, delta_s: torch.Tensor,
                         len_q: int, len_k: int, sm_scale: float, causal: bool = False,
-                        return_lse: bool = False, lamb: torch.Tensor | None = None):
+                        return_lse: bool = False, lamb: torch.Tensor | None = None,
+                        q_tiles=None, mean_slot: str = "mask"):
     """Flash-style forward on de-quantised operands with the reference's P re-quantisation.
 
     qd  [B,Hq,Nq_pad,D]  fp32 = dequantised Q codes
@@ -129,6 +130,14 @@ def attention_quantised(qd: torch.Tensor, kd: torch.Tensor, vtd: torch.Tensor, d
     gets ``lamb * (score of its group's mean slot)`` added before masking, the causal mask works on the
     logical token of each packed key (:273-281, :921-934) and the mean slot itself is masked out
     (:878-881, per-block-mean variant).
+    mean_slot (K-packing mode only): "mask" = the per-block-mean kernels, the slot is masked out;
+    "first" = the other kernel variant (:882-888): the slot takes the (masked) score of the group's first token
+    where ``can_use_mean_slot`` (:855-871) allows, its probability multiplies the slot's V row (the first
+    token's FP4 remainder under ``v_trick``) but is left out of the row sum (softmax_fused.h:48-64).
+    q_tiles (or None): qd holds only these 128-row query tiles of a longer sequence of ``len_q``
+    tokens (tile i of qd is query tile ``q_tiles[i]``; delta_s has the same rows); all rows of the
+    given tiles are returned, the caller drops those beyond ``len_q``.  Lets a test check a few query
+    tiles of a benchmark-sized problem against all of its keys.
     Returns O [B,Hq,len_q,D] fp32 (callers round to bf16) and optionally the log-sum-exp
     (natural log, of the smoothed scores) [B,Hq,len_q].
     """
@@ -148,6 +157,8 @@ def attention_quantised(qd: torch.Tensor, kd: torch.Tensor, vtd: torch.Tensor, d
     m = torch.full((B, Hq, nqb, BLOCK), -math.inf)
     l = torch.zeros(B, Hq, nqb, BLOCK)
     qpos = torch.arange(Nq).reshape(nqb, BLOCK)
+    if q_tiles is not None:
+        qpos = torch.as_tensor(list(q_tiles)).reshape(nqb, 1) * BLOCK + torch.arange(BLOCK).reshape(1, BLOCK)
     for j in range(nkb - 1, -1, -1):                       # fwd_mainloop.cu:575,1080 (last tile first)
         ks = kd[:, :, j * BLOCK:(j + 1) * BLOCK]           # [B,H,128,D]
         S = torch.einsum("bhqrd,bhkd->bhqrk", q4, ks)
@@ -164,18 +175,34 @@ def attention_quantised(qd: torch.Tensor, kd: torch.Tensor, vtd: torch.Tensor, d
         mask = (kpos >= len_k)[None, None, :].expand(nqb, BLOCK, BLOCK)
         if causal:                                         # fwd_mainloop.cu:926
             mask = mask | (ktok[None, None, :] >= (qpos[:, :, None] + 1 + len_k_logical - len_q))
-        if lamb is not None:                               # the mean slot carries no token (:878-881)
-            mask = mask | (kpos % 16 == 0)[None, None, :]
+        is_slot = (kpos % 16 == 0)
+        if lamb is not None and mean_slot == "mask":       # the mean slot carries no token (:878-881)
+            mask = mask | is_slot[None, None, :]
         if causal and bool(mask.all()):
             continue                                       # tile never visited (get_n_block_max :305-324)
         S = S.masked_fill(mask, -math.inf)
+        if lamb is not None and mean_slot == "first":      # set_mean_slot_to_first_score, :847-891
+            first = S.reshape(B, Hq, nqb, BLOCK, BLOCK // 16, 16)[..., 1]
+            usable = torch.ones(nqb, BLOCK, BLOCK // 16, dtype=torch.bool)
+            if causal:
+                qk = qpos + len_k_logical - len_q                              # query_key_pos
+                col = kpos[0::16]                                              # the slots' packed positions
+                usable = (col[None, None, :] < len_k) & (qk[:, :, None] >= 0) & \
+                         ((col[None, None, :] // 16) < (qk[:, :, None].clamp(min=0) // 15))
+            slot_val = torch.where(usable[None, None], first, torch.full_like(first, -math.inf))
+            S = S.clone().reshape(B, Hq, nqb, BLOCK, BLOCK // 16, 16)
+            S[..., 0] = slot_val
+            S = S.reshape(B, Hq, nqb, BLOCK, BLOCK)
         bm = S.reshape(B, Hq, nqb, BLOCK, BLOCK // 16, 16).amax(dim=-1)       # softmax_fused.h:113-121
         m_new = torch.maximum(m, bm.amax(dim=-1))
         m_fin = torch.where(torch.isinf(m_new), torch.zeros_like(m_new), m_new)
         alpha = torch.exp2((m - m_fin) * c)                                   # :130 (0 on the first tile)
         max_scaled = m_fin * c + LOG2_INV_2688
         P = torch.exp2(S * c - max_scaled[..., None])                         # :138  in (0, 2688]
-        l = l * alpha + P.sum(dim=-1)                                         # :135,139 (unquantised P)
+        if lamb is not None and mean_slot == "first":                         # the slot is not a token: no row-sum share
+            l = l * alpha + P.masked_fill(is_slot[None, None, None, None, :], 0.0).sum(dim=-1)
+        else:
+            l = l * alpha + P.sum(dim=-1)                                     # :135,139 (unquantised P)
         sb = torch.exp2(bm * c - max_scaled[..., None] + LOG2_INV_6)          # :142-144
         P6 = P.reshape(B, Hq, nqb, BLOCK, BLOCK // 16, 16)
         Pn = torch.where(sb[..., None] > 0, P6 / sb[..., None], torch.zeros_like(P6))  # :148-153
@@ -185,10 +212,11 @@ def attention_quantised(qd: torch.Tensor, kd: torch.Tensor, vtd: torch.Tensor, d
         O = O * alpha[..., None] + torch.einsum("bhqrk,bhdk->bhqrd", Pq, vt)  # softmax_fused.h:183
         m = m_new
     inv = torch.where((l == 0) | torch.isnan(l), torch.zeros_like(l), 1.0 / l)  # :167
-    out = (O * inv[..., None]).reshape(B, Hq, Nq, D)[:, :, :len_q]
+    keep = Nq if q_tiles is not None else len_q
+    out = (O * inv[..., None]).reshape(B, Hq, Nq, D)[:, :, :keep]
     if not return_lse:
         return out
-    lse = (m * sm_scale + torch.log(l / 2688.0)).reshape(B, Hq, Nq)[:, :, :len_q]
+    lse = (m * sm_scale + torch.log(l / 2688.0)).reshape(B, Hq, Nq)[:, :, :keep]
     return out, lse
 
 
@@ -261,37 +289,61 @@ def pack_k(k_s: torch.Tensor):
     return packed.reshape(B, H, G * 16, D), lamb.reshape(B, H, G * 16)
 
 
-def pack_v(v: torch.Tensor):
-    """api.py:150-177 with split_first=False: a zero row in every mean slot."""
+def pack_v(v: torch.Tensor, split_first: bool = False):
+    """api.py:150-177.  ``split_first=False``: a zero row in every mean slot.  ``split_first=True`` (the
+    ``v_trick``): the group's first token is stored twice over - slot 1 holds its value as the V^T quantiser will
+    round it (FP4 along tokens, with the slot still zero), slot 0 the remainder - so that a kernel which gives slot 0
+    the first token's probability recovers that token's V to two FP4 terms."""
     B, H, _, D = v.shape
     x = pad_tokens(v, 15)
     G = x.shape[-2] // 15
     xb = x.reshape(B, H, G, 15, D)
-    packed = torch.cat([torch.zeros(B, H, G, 1, D, dtype=v.dtype), xb], dim=-2)
-    return packed.reshape(B, H, G * 16, D)
+    zero = torch.zeros(B, H, G, 1, D, dtype=v.dtype)
+    if not split_first:
+        return torch.cat([zero, xb], dim=-2).reshape(B, H, G * 16, D)
+    base = pad_tokens(torch.cat([zero, xb], dim=-2).reshape(B, H, G * 16, D))
+    rounded = torch.from_numpy(nvfp4.fake_quant(base.float().transpose(-1, -2).contiguous().numpy()))
+    rounded = rounded.transpose(-1, -2)[:, :, :G * 16].to(v.dtype).reshape(B, H, G, 16, D)
+    hi = rounded[:, :, :, 1]
+    slot = (xb[:, :, :, 0].float() - hi.float()).to(v.dtype)
+    split = xb.clone()
+    split[:, :, :, 0] = hi
+    return torch.cat([slot.unsqueeze(-2), split], dim=-2).reshape(B, H, G * 16, D)
 
 
 def sageattn4_emulated(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool = False,
-                       sm_scale: float | None = None, mode: str = "exact"):
-    """The fork's K-packing pipeline (api.py:179-205, 250-288) with per_block_mean=True and
-    v_trick=False, on HND bf16 CPU tensors."""
+                       sm_scale: float | None = None, mode: str = "exact", per_block_mean: bool = True,
+                       v_trick: bool | None = None):
+    """The fork's K-packing pipeline (api.py:179-205, 250-288) on HND bf16 CPU tensors.  ``per_block_mean`` selects
+    the kernel variant (per-128-token Q mean and a masked mean slot, or whole-sequence Q mean and a mean slot that
+    takes the first token's score); ``v_trick`` (default ``not per_block_mean``, api.py:180-181) the V layout."""
     D = q.shape[-1]
     Lq, Lk = q.shape[-2], k.shape[-2]
     if sm_scale is None:
         sm_scale = D ** -0.5
+    if v_trick is None:
+        v_trick = not per_block_mean
     g = q.shape[1] // k.shape[1]
     k_s, _ = smooth_k(k)
-    q_s, qm = q_block_mean(pad_tokens(q))
+    q_pad = pad_tokens(q)
+    if per_block_mean:
+        q_s, qm = q_block_mean(q_pad)
+    else:
+        qm = q_pad.mean(dim=-2, keepdim=True)
+        q_s = q_pad - qm
     k_p, lamb = pack_k(k_s)
-    v_p = pack_v(v)
+    v_p = pack_v(v, split_first=v_trick)
     k_p = pad_tokens(k_p)
     lamb = pad_tokens(lamb.unsqueeze(-1)).squeeze(-1)
     k_rep = k_p.repeat_interleave(g, dim=1) if g > 1 else k_p
     delta_s = torch.matmul(qm, k_rep.transpose(-2, -1)).to(torch.float32)     # from the unrounded packed K
+    if not per_block_mean:
+        delta_s = delta_s.expand(-1, -1, q_pad.shape[-2] // BLOCK, -1)
     qd = dequant(*quant_rows(q_s, mode))
     kd = dequant(*quant_rows(k_p, mode))
     vtd = dequant(*quant_v_transposed(pad_tokens(v_p), mode))
-    out = attention_quantised(qd, kd, vtd, delta_s, Lq, logical_to_packed_len(Lk), sm_scale, is_causal, lamb=lamb)
+    out = attention_quantised(qd, kd, vtd, delta_s, Lq, logical_to_packed_len(Lk), sm_scale, is_causal, lamb=lamb,
+                              mean_slot="mask" if per_block_mean else "first")
     return out.to(q.dtype)
 
 

@@ -6,10 +6,12 @@ build it, and every call checks the returned status.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 _HERE = Path(__file__).resolve().parent
-LIB_PATH = _HERE / "libsage3_b200.so"
+# SAGE3_B200_LIB points at another build of the same library (A/B timing of kernel variants); it must export the same C ABI
+LIB_PATH = Path(os.environ.get("SAGE3_B200_LIB") or (_HERE / "libsage3_b200.so"))
 
 OK, ERR_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE_WAIT, ERR_TOO_LARGE = range(6)
 
@@ -62,7 +64,8 @@ class FwdArgs(C.Structure):
 class PackArgs(C.Structure):
     _fields_ = [("shape", Shape), ("k", Tensor), ("v", Tensor), ("smooth_k", C.c_int32),
                 ("km_in", C.c_void_p), ("km", C.c_void_p), ("k_packed", C.c_void_p), ("v_packed", C.c_void_p),
-                ("k_lambda", C.c_void_p), ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t)]
+                ("k_lambda", C.c_void_p), ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t),
+                ("split_first", C.c_int32)]
 
 
 class VarlenArgs(C.Structure):
@@ -78,7 +81,7 @@ class VarlenArgs(C.Structure):
 EXPORTS = ("sage3_version", "sage3_status_string", "sage3_last_cuda_error", "sage3_buffer_sizes",
            "sage3_quant_qkv", "sage3_attn_fwd", "sage3_attention", "sage3_read_device_status",
            "sage3_k_mean_static", "sage3_packed_rows", "sage3_packed_len", "sage3_pack_kv",
-           "sage3_attn_fwd_packed", "sage3_attention_varlen")
+           "sage3_attn_fwd_packed", "sage3_attention_varlen", "sage3_fp4_mma_peak", "sage3_selftest_bounded_wait")
 
 _lib = None
 
@@ -105,8 +108,10 @@ def load() -> C.CDLL:
     lib.sage3_packed_rows.argtypes = [C.c_int]
     lib.sage3_packed_len.argtypes = [C.c_int]
     lib.sage3_pack_kv.argtypes = [C.POINTER(PackArgs), C.c_void_p]
-    lib.sage3_attn_fwd_packed.argtypes = [C.POINTER(AttnArgs), C.c_void_p, C.c_void_p]
+    lib.sage3_attn_fwd_packed.argtypes = [C.POINTER(AttnArgs), C.c_void_p, C.c_int32, C.c_void_p]
     lib.sage3_attention_varlen.argtypes = [C.POINTER(VarlenArgs), C.c_void_p]
+    lib.sage3_fp4_mma_peak.argtypes = [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.POINTER(C.c_double)]
+    lib.sage3_selftest_bounded_wait.argtypes = [C.c_void_p, C.c_void_p]
     for name in EXPORTS:
         getattr(lib, name)            # raises AttributeError if an export is missing
     _lib = lib

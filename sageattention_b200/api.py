@@ -85,6 +85,7 @@ class QuantizedQKV:
     delta_s_rows: int
     k_lambda: Optional[torch.Tensor] = None          # K-packing mode: fp32 [B,Hkv,Tk*128]
     nk_slots: Optional[int] = None                   # K-packing mode: occupied key slots (<= Nk)
+    mean_slot_first: bool = False                    # K-packing mode: the mean slot takes the first token's score
 
 
 def quantize_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",
@@ -179,8 +180,8 @@ def fp4_attention(qz: QuantizedQKV, sm_scale: Optional[float] = None, is_causal:
     with torch.cuda.device(dev):
         if qz.k_lambda is not None:
             a.shape = _lib.Shape(B, Hq, Hkv, Nq, int(qz.nk_slots), D)
-            _lib.check(lib.sage3_attn_fwd_packed(C.byref(a), qz.k_lambda.data_ptr(), _stream_ptr(dev)),
-                       "sage3_attn_fwd_packed")
+            _lib.check(lib.sage3_attn_fwd_packed(C.byref(a), qz.k_lambda.data_ptr(), int(qz.mean_slot_first),
+                                                 _stream_ptr(dev)), "sage3_attn_fwd_packed")
         else:
             _lib.check(lib.sage3_attn_fwd(C.byref(a), _stream_ptr(dev)), "sage3_attn_fwd")
         if check_status:
@@ -188,10 +189,12 @@ def fp4_attention(qz: QuantizedQKV, sm_scale: Optional[float] = None, is_causal:
     return (out, lse) if return_lse else out
 
 
-def pack_kv(k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND", smooth_k: bool = True):
+def pack_kv(k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND", smooth_k: bool = True,
+            split_first: bool = False):
     """K-packing preprocessing (``quant_pack_k`` / ``quant_pack_v`` and the K centring of
     ``sageattn4/api.py:122-177,184``): every 15 key tokens become 16 slots (FP4-rounded group mean + 15
-    residuals), V gets a zero row per mean slot.  Returns ``(k_packed, v_packed, k_lambda, km)`` with the
+    residuals), V gets a zero row per mean slot - or, with ``split_first`` (the reference's ``v_trick``), the
+    group's first V row split into its FP4 rounding (slot 1) and the remainder (slot 0).  Returns ``(k_packed, v_packed, k_lambda, km)`` with the
     packed tensors in HND ``[B,Hkv,16*ceil(Nk/15),D]`` and ``k_lambda`` fp32 padded to a multiple of 128."""
     lib = _lib.load()
     _check_device(k)
@@ -214,6 +217,7 @@ def pack_kv(k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND", smooth
     a.km = km.data_ptr() if km is not None else None
     a.k_packed, a.v_packed, a.k_lambda = kp.data_ptr(), vp.data_ptr(), lam.data_ptr()
     a.scratch, a.scratch_bytes = scratch.data_ptr(), scratch.numel()
+    a.split_first = int(bool(split_first))
     with torch.cuda.device(dev):
         _lib.check(lib.sage3_pack_kv(C.byref(a), _stream_ptr(dev)), "sage3_pack_kv")
     return kp, vp, lam, km
@@ -225,22 +229,25 @@ def sageattn4_blackwell(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tenso
                         check_status: bool = False, **kwargs):
     """The fork's K-packing operator (``sageattn4_blackwell``, ``sageattn4/api.py:250-288``): K is centred,
     packed 15 -> 16 (group mean + residuals) and the kernel restores every score as
-    ``q.residual + lambda * q.mean``.  Supported: ``quant_block=16``, ``per_block_mean=True`` and the V layout
-    that goes with it (``v_trick`` False, a zero row per mean slot)."""
+    ``q.residual + lambda * q.mean``.  ``per_block_mean`` selects the kernel variant as in the reference
+    (``fwd_mainloop.cu:878-888``): True = per-128-token Q mean, the mean slot is masked out; False =
+    whole-sequence Q mean, the mean slot takes the first token's score.  ``v_trick`` (default
+    ``not per_block_mean``, ``api.py:180-181``) selects the split-first V layout.  ``quant_block`` must be 16."""
     lib = _lib.load()
     if attn_mask is not None:
         raise NotImplementedError("attn_mask is not supported (the reference ignores it, api.py:250)")
     if quant_block != 16:
         raise AssertionError("quant_block must be 16")                                   # api.py:251
-    if not per_block_mean or v_trick:
-        raise NotImplementedError("the K-packing mode is built for per_block_mean=True / v_trick=False")
     if q.shape[-1] not in (64, 128):
         raise ValueError(f"Unsupported Headdim {q.shape[-1]}")
-    kp, vp, lam, _ = pack_kv(k, v, tensor_layout, smooth_k=True)
+    if v_trick is None:
+        v_trick = not per_block_mean
+    kp, vp, lam, _ = pack_kv(k, v, tensor_layout, smooth_k=True, split_first=bool(v_trick))
     if tensor_layout == "NHD":
         kp, vp = kp.transpose(1, 2), vp.transpose(1, 2)          # views; the quantiser takes strides
-    qz = quantize_qkv(q, kp, vp, tensor_layout, per_block_mean=True, smooth_k=False)
+    qz = quantize_qkv(q, kp, vp, tensor_layout, per_block_mean=bool(per_block_mean), smooth_k=False)
     qz.k_lambda = lam
+    qz.mean_slot_first = not per_block_mean
     Nk = k.shape[2] if tensor_layout == "HND" else k.shape[1]
     qz.nk_slots = lib.sage3_packed_len(Nk)
     return fp4_attention(qz, sm_scale=sm_scale, is_causal=is_causal, tensor_layout=tensor_layout,
@@ -426,9 +433,15 @@ def sageattn_from_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: O
         if h0 == h1:
             continue
         with torch.cuda.stream(s_in):
-            qd = q[:, h0 * g:h1 * g].to(dev, non_blocking=True)
-            kd = k[:, h0:h1].to(dev, non_blocking=True)
-            vd = v[:, h0:h1].to(dev, non_blocking=True)
+            # one copy per batch entry: q[b, h0:h1] is one contiguous block of a [B,H,N,D] tensor, q[:, h0:h1] is not
+            # (for B > 1 a strided host-to-device copy falls back to a slow path)
+            qd = torch.empty((B, (h1 - h0) * g, Nq, D), dtype=q.dtype, device=dev)
+            kd = torch.empty((B, h1 - h0) + tuple(k.shape[2:]), dtype=k.dtype, device=dev)
+            vd = torch.empty_like(kd)
+            for b in range(B):
+                qd[b].copy_(q[b, h0 * g:h1 * g], non_blocking=True)
+                kd[b].copy_(k[b, h0:h1], non_blocking=True)
+                vd[b].copy_(v[b, h0:h1], non_blocking=True)
             ev_in = torch.cuda.Event()
             ev_in.record(s_in)
         # groups alternate between two compute streams: the attention kernel is persistent (one CTA per SM), so
@@ -441,7 +454,8 @@ def sageattn_from_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: O
             ev_run.record(s_run)
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_run)
-            out[:, h0 * g:h1 * g].copy_(od, non_blocking=True)
+            for b in range(B):
+                out[b, h0 * g:h1 * g].copy_(od[b], non_blocking=True)
         keep.append((qd, kd, vd, od))
     done = torch.cuda.Event()
     done.record(s_out)

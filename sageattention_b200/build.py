@@ -14,7 +14,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libsage3_b200.so"
-SOURCES = ["quant.cu", "pack.cu", "delta_s.cu", "attn.cu", "attn_varlen.cu", "cabi.cu"]
+SOURCES = ["quant.cu", "pack.cu", "delta_s.cu", "attn.cu", "attn_varlen.cu", "peak.cu", "selftest.cu", "cabi.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 

@@ -1,41 +1,49 @@
 // FP4 (NVFP4 block-scaled) flash-attention forward for B200 (sm_100a): TMA -> shared memory ->
 // tcgen05.mma kind::mxf4nvf4 with accumulators in tensor memory -> online softmax in registers
-// with two-level FP4 re-quantisation of P -> second block-scaled MMA for P.V.
+// with two-level FP4 re-quantisation of P -> second block-scaled MMA for P.V, accumulated in tensor memory.
 //
 // Replaces the reference's sm_120-only mma.sync kernel (sageattn4/blackwell/fwd_kernel.cu:45-200,
 // fwd_mainloop.cu:639-1125, softmax_fused.h:39-187, fwd_epilogue.cu:30-183) and its host launcher
 // (fwd_kernel.cu:202-293).  Arithmetic follows the reference step by step:
 //   S = delta_s + Q^ K^T                              fwd_mainloop.cu:766-794, 908-919
 //   masks (key padding, bottom-right causal)          fwd_mainloop.cu:921-964
-//   online softmax with P in (0, 448*6], per-16-key scale = blockmax/6 stored as E4M3, P/scale
-//   stored as E2M1                                    softmax_fused.h:107-153, fwd_mainloop.cu:967-1002
-//   O = O * alpha + P^ V^ with a fresh accumulator per key tile     softmax_fused.h:175-187
+//   online softmax, per-16-key scale = blockmax/6 stored as E4M3, P/scale stored as E2M1
+//                                                     softmax_fused.h:107-153, fwd_mainloop.cu:967-1002
+//   O = sum over key tiles of P^ V^, rescaled when the row maximum moves     softmax_fused.h:175-187
 //   O /= l, bf16                                      softmax_fused.h:156-173, fwd_epilogue.cu:103-147
 // Key tiles are visited from the last to the first as the reference does (fwd_mainloop.cu:575).
+//
+// Where this kernel departs from the reference's arithmetic (inside the parity tolerance, see the tests):
+// the reference keeps O in registers and multiplies it by 2^(m_old - m_new) after EVERY key tile; here O stays in
+// tensor memory, the P.V MMAs accumulate into it, and it is rescaled only when a row's maximum has grown by more
+// than 2^kLazyLog2 since the reference maximum was last set.  Until then P is computed against that (stale)
+// reference maximum; so that it still fits the E4M3 block scales, P is normalised to (0, 2688 / 2^kLazyLog2]
+// against the reference maximum instead of (0, 2688] against the true one.  Block scales are powers of two apart
+// from the reference's unless they fall below the E4M3 normal range (blocks whose maximum is under 2^-11.8 of the
+// row's reference maximum instead of 2^-14.8).
 //
 // One persistent CTA per SM walks a static list of work items (round r: item r*grid + i, odd rounds in
 // reverse CTA order; causal items sorted by falling cost over all heads);
 // an item is TWO adjacent 128-row query tiles of one head, which share every K / V tile.  All
 // barrier phases keep counting across items, so the loads and the first Q.K^T of the next item are
-// under way while the last softmax, fold and output store of the current one finish.  12 warps:
-//   warps 0-3   softmax warpgroup of query tile 0: thread r owns score row r (tensor-memory lane r)
-//               and the O row in registers.  Per key tile: pass 1 scans S for the 16-key block
-//               maxima, pass 2 turns S into P^; every tensor-memory load is issued one block ahead
-//               of its use; then the P.V product is folded into O.  At the end of an item O / l goes
-//               out as bf16 (D=128: through a swizzled staging tile and TMA stores).
-//   warps 4-7   the same for query tile 1; the two warpgroups run half a period apart, so one does
-//               softmax arithmetic while the other waits for its MMAs
+// under way while the last softmax and the output store of the current one finish.  12 warps:
+//   warps 0-3   softmax warpgroup of query tile 0: thread r owns score row r (tensor-memory lane r).  Per key
+//               tile it copies its 128 scores from tensor memory into registers and releases the score buffer at
+//               once (the Q.K^T of the other query tile is issued into it while this tile is worked on), then:
+//               16-key block maxima, block scales, exponentials, E2M1 codes of P^ into shared memory.  It never
+//               waits for the P.V product: the MMA accumulates into the tile's O in tensor memory.  At the end of
+//               an item O / l goes out as bf16 (D=128: through a swizzled staging tile and TMA stores).
+//   warps 4-7   the same for query tile 1; the two warpgroups settle half a period apart
 //   warp  8     TMA producer (Q tiles per item, then a ring of K and V stages; scale factors and the
 //               delta_s rows by plain bulk copies)
-//   warp  9     QK issuer (one lane): scale-factor copies, rank-1 delta_s MMA and Q.K^T MMAs, both tiles
+//   warp  9     QK issuer (one lane): scale-factor copies, rank-1 delta_s MMA and Q.K^T MMAs, both tiles in turn
+//               into the ONE score buffer
 //   warp 10     turns each delta_s row (128 bf16) into the B operand of a rank-1 bf16 MMA
 //               (ones x delta_s) that initialises the score accumulator, so the softmax warps never
 //               touch delta_s
-//   warp 11     PV issuer (one lane): scale-factor copies and P.V MMAs for both tiles; the MMA over keys 0-63
-//               of a tile is issued as soon as the softmax has written that half of P^ (its own barrier)
+//   warp 11     PV issuer (one lane): scale-factor copies and P.V MMAs, O_t += P^_t V^
 //
-// Tensor memory (512 columns): S0 [0,128) S1 [128,256) PV product [256,256+D) (shared by both
-// tiles, drained into registers right after each PV MMA) and 48 columns of scale factors.
+// Tensor memory (512 columns): O0 [0,D) O1 [D,2D) S [2D,2D+128) and 48 columns of scale factors.
 //
 // Every wait on an mbarrier is bounded; if one gives up the CTA records a code in *status, waits
 // (bounded) for its own copies and MMAs in flight, frees its tensor memory and returns.
@@ -75,16 +83,18 @@ constexpr int kAttnThreads = 384;
 // Register hand-over (setmaxnreg) moves registers inside the pool the CTA was LAUNCHED with; a request beyond
 // it would block forever, so the split is checked here.  kLaunchRegs is what the compiler allocates under
 // __launch_bounds__(384, 1).
-// The split was chosen by measurement per head dimension (D=64 runs 9 % faster with the second one).
 constexpr int kLaunchRegs = 168;
 template <int D> struct RegSplit { static constexpr int softmax = 224, role = 56; };
-template <> struct RegSplit<64> { static constexpr int softmax = 232, role = 40; };
-static_assert(256 * RegSplit<128>::softmax + 128 * RegSplit<128>::role <= kAttnThreads * kLaunchRegs &&
-              256 * RegSplit<64>::softmax + 128 * RegSplit<64>::role <= kAttnThreads * kLaunchRegs,
+static_assert(256 * RegSplit<128>::softmax + 128 * RegSplit<128>::role <= kAttnThreads * kLaunchRegs,
               "setmaxnreg split exceeds the CTA's register pool");
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLog2Inv2688 = -11.392317422778762f;   // log2(1 / (448 * 6))  softmax_fused.h:33
 constexpr float kLog2Inv6 = -2.584962500721156f;       // log2(1 / 6)          softmax_fused.h:34
+// O in tensor memory is rescaled only when a row maximum has grown by more than this (log2 units of P) since
+// the row's reference maximum was set; P is normalised to 2688 / 2^kLazyLog2 at the reference maximum so that
+// it cannot exceed 2688 (block scale 448, the E4M3 maximum) before that happens
+constexpr float kLazyLog2 = 3.0f;
+constexpr float kLog2InvTop = kLog2Inv2688 + kLazyLog2;
 
 template <int D>
 struct Smem {
@@ -110,8 +120,7 @@ struct Smem {
   static constexpr int lam = dsraw + kStages * 2 * 256;   // [2 * kStages][128] f32: lambda of the key slots (K-packing
                                                           // mode), arrives with the K stage; twice as many slots as
                                                           // stages because the softmax reads it after the stage is freed
-  static constexpr int stats = lam + 2 * kStages * 512;   // [2][8 blocks][128 rows] float2 (exponent offset, scale)
-  static constexpr int bars = stats + 2 * 8 * 128 * 8;
+  static constexpr int bars = lam + 2 * kStages * 512;
   // output staging for the TMA store: [2 tiles][D/64 column halves][128 rows x 128 bytes], 128-byte swizzle
   static constexpr int kOStage = 128 * 128;
   static constexpr int ostage = (bars + 512 + 1023) / 1024 * 1024;
@@ -126,14 +135,14 @@ struct Bars {            // byte offsets inside the barrier block
   static constexpr int v_full = k_empty + 8 * kStages;
   static constexpr int v_empty = v_full + 8 * kStages;
   static constexpr int ds_ready = v_empty + 8 * kStages;
-  static constexpr int s_full = ds_ready + 8 * kStages;   // [2]
-  static constexpr int p_full = s_full + 16;              // [2]
-  static constexpr int o_full = p_full + 16;              // [2]
-  static constexpr int o_free = o_full + 16;
-  static constexpr int drain = o_free + 8;                // [2] the issuers' last commit when giving up
-  static constexpr int p_half = drain + 16;               // [2] first 64 keys of P^ (and their scales) written
-  static constexpr int epi = p_half + 16;                 // [2] rendezvous of a softmax warpgroup around its output staging
-  static constexpr int tmem_slot = epi + 16;             // u32 written by tcgen05.alloc
+  static constexpr int s_full = ds_ready + 8 * kStages;   // [2] Q.K^T of tile t is in the score buffer
+  static constexpr int s_free = s_full + 16;              // the score buffer has been copied into registers
+  static constexpr int p_full = s_free + 8;               // [2] P^ and its scales written (O rescaled if it had to be)
+  static constexpr int pv_done = p_full + 16;             // [2] P.V MMAs of tile t complete: P^ may be rewritten, O_t is current
+  static constexpr int o_free = pv_done + 16;             // [2] the epilogue has read O_t out of tensor memory
+  static constexpr int drain = o_free + 16;               // [2] the issuers' last commit when giving up
+  static constexpr int epi = drain + 16;                  // [2] rendezvous of a softmax warpgroup around its output staging
+  static constexpr int tmem_slot = epi + 16;              // u32 written by tcgen05.alloc
   static constexpr int abort_flag = tmem_slot + 8;
   static constexpr int run_flag = abort_flag + 4;
 };
@@ -149,26 +158,13 @@ struct KParams {
   float scale_log2;      // sm_scale * log2(e)
   const float* lam;      // K-packing mode: lambda per key slot, fp32 [B,Hkv,Tk*128]; Nk is the packed length
   int Nk_log;            // number of key tokens (= Nk unless packed)
+  bool slot_first;       // K-packing mode: the mean slot takes the first token's score instead of being masked
   bool o_token_first;    // output tensor map: coordinates (d, token, head, batch) or (d, head, token, batch)
 #if SAGE3_VARLEN_BUILD
   const int *cu_q, *cu_k; // token offsets of the sequences (device int32 [B+1]); Nq, Nk, Tq, Tk then describe the
                           // LONGEST sequence, i.e. the rectangular operand layouts
 #endif
 };
-
-// Bounded wait on an mbarrier phase; also gives up as soon as any CTA has reported a failure.  A failing poll
-// parks the thread for about 1.5 us (kHinted: about 4 us), so the limit is 3 to 8 seconds; which flavour is
-// faster was measured per role: the shorter park costs issue slots but reacts sooner.
-template <bool kHinted>
-__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_s, int* status, int code) {
-  for (uint32_t i = 0; i < (1u << 21); ++i) {
-    if (mbar_try_wait<kHinted ? 20000 : 0>(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && (*abort_s != 0 || *reinterpret_cast<volatile int*>(status) != 0)) break;
-  }
-  *abort_s = 1;
-  atomicCAS(status, 0, code);
-  return false;
-}
 
 // ---- packed fp32x2 arithmetic (one issue slot for two elements) and 3-input max
 __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
@@ -199,23 +195,18 @@ __device__ __forceinline__ float max16(const uint32_t* r) {
   return fmaxf(fmax3(a, b, c), fmax3(d, e, __uint_as_float(r[15])));
 }
 
-// One key tile for one score row (one thread), in two passes over tensor memory.  Straight-line code
-// (no branch when kMask is false) so that the scheduler can overlap the exp2 stream of one block with
-// the adds and conversions of its neighbour; every load is issued one 16-key block before its use.
-//   m, l      running row maximum (raw score units) and row sum (of P = 2^(s*c - m*c) * 2688)
-//   st        this thread's column of the shared scratch: per block (exponent offset, scale)
-// Pass 1: block maxima -> new row maximum, rescale factor alpha = 2^((m_old - m_new) * c) (returned),
-// per-block scales (P blockmax / 6) as E4M3 bytes for the PV MMA (`sfp`) and, unrounded, in `st`.
+// The softmax of one key tile works on one score row (128 values) held in the registers of one thread; every
+// loop below is fully unrolled so that the row never leaves the register file.
+
 // K-packing mode (fwd_mainloop.cu:796-845, 878-881): a block of 16 keys is one group - slot 0 holds the
 // score of the group mean, which every other score of the group gets added lambda times; the slot itself
-// carries no token and is masked out.  Done once, in pass 1, which writes the corrected scores back to
-// tensor memory for pass 2.
-__device__ __forceinline__ void apply_lambda(uint32_t (&r)[16], const float4 (&lq)[4]) {
+// carries no token and is masked out.
+__device__ __forceinline__ void apply_lambda(uint32_t* r, const float* lam16) {
   const float s0 = __uint_as_float(r[0]);
   const float2 s02 = make_float2(s0, s0);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const float4 l4 = lq[i];
+    const float4 l4 = reinterpret_cast<const float4*>(lam16)[i];
     const float2 a = ffma2(make_float2(l4.x, l4.y), s02, make_float2(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1])));
     const float2 b = ffma2(make_float2(l4.z, l4.w), s02, make_float2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])));
     r[4 * i] = __float_as_uint(a.x); r[4 * i + 1] = __float_as_uint(a.y);
@@ -224,126 +215,76 @@ __device__ __forceinline__ void apply_lambda(uint32_t (&r)[16], const float4 (&l
   r[0] = 0xff800000u;
 }
 
-template <bool kMask, bool kPacked>
-__device__ __forceinline__ float softmax_pass1_impl(const uint32_t tm_S, const float c, float& m, float2* st,
-                                                    uint2& sfp, const int n0, const int key_lim, const float* lam_s) {
-  uint32_t ra[16], rb[16];
-  float bm[8];
-  float4 la[4], lb[4];                                      // lambdas of the block in ra / rb, fetched one block ahead
-  tmem_ld16(tm_S, ra);
-  if (kPacked) {
+// 128 score columns of this thread's tensor-memory lane -> registers
+__device__ __forceinline__ void load_scores(const uint32_t tm_S, uint32_t (&s)[128]) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) la[i] = reinterpret_cast<const float4*>(lam_s)[i];
-  }
-#pragma unroll
-  for (int blk = 0; blk < 8; blk += 2) {
-    if (kPacked) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) lb[i] = reinterpret_cast<const float4*>(lam_s + (blk + 1) * 16)[i];
-    }
-    tmem_wait_ld();
-    tmem_ld16(tm_S + (blk + 1) * 16, rb);
-    if (kPacked) {
-      apply_lambda(ra, la);
-      tmem_st16(tm_S + blk * 16, ra);
-    }
-    if (kMask) {
-#pragma unroll
-      for (int i = 0; i < 16; ++i) ra[i] = (n0 + blk * 16 + i > key_lim) ? 0xff800000u : ra[i];
-    }
-    bm[blk] = max16(ra);
-    if (kPacked && blk + 2 < 8) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) la[i] = reinterpret_cast<const float4*>(lam_s + (blk + 2) * 16)[i];
-    }
-    tmem_wait_ld();
-    if (blk + 2 < 8) tmem_ld16(tm_S + (blk + 2) * 16, ra);
-    if (kPacked) {
-      apply_lambda(rb, lb);
-      tmem_st16(tm_S + (blk + 1) * 16, rb);
-    }
-    if (kMask) {
-#pragma unroll
-      for (int i = 0; i < 16; ++i) rb[i] = (n0 + (blk + 1) * 16 + i > key_lim) ? 0xff800000u : rb[i];
-    }
-    bm[blk + 1] = max16(rb);
-  }
-  if (kPacked) tmem_wait_st();
-  const float m_new = fmax3(fmax3(bm[0], bm[1], bm[2]), fmax3(bm[3], bm[4], bm[5]), fmax3(bm[6], bm[7], m));
-  const float m_fin = (m_new == -INFINITY) ? 0.f : m_new;
-  const float alpha = ex2_approx((m - m_fin) * c);          // 0 on the first tile
-  const float off = fmaf(m_fin, c, kLog2Inv2688);           // P = 2^(s*c - off) in (0, 2688]
-  m = m_new;
-  float sb[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const float e = fmaf(bm[i], c, kLog2Inv6);
-    sb[i] = ex2_approx(e - off);
-    st[i * 128] = make_float2((bm[i] == -INFINITY) ? 0.f : -e, sb[i]);
-  }
-  sfp.x = f32x2_to_e4m3x2(sb[0], sb[1]) | (f32x2_to_e4m3x2(sb[2], sb[3]) << 16);   // keys 0-63 of the tile
-  sfp.y = f32x2_to_e4m3x2(sb[4], sb[5]) | (f32x2_to_e4m3x2(sb[6], sb[7]) << 16);   // keys 64-127
-  return alpha;
+  for (int q = 0; q < 4; ++q) tmem_ld32(tm_S + 32 * q, *reinterpret_cast<uint32_t (*)[32]>(&s[32 * q]));
+  tmem_wait_ld();
 }
 
-// Pass 2: P / blockscale = 2^(s*c - (bm*c + log2(1/6))) in [0, 6] -> E2M1 codes into the swizzled P^ tile;
-// the row sum uses the unrounded values times the unrounded block scale (softmax_fused.h:135-153).
-template <bool kMask, bool kPacked>
-__device__ __forceinline__ void softmax_pass2_impl(const uint32_t tm_S, const float c, const float alpha, float& l,
-                                                   const float2* st, uint8_t* p_row, const int swz, const int n0,
-                                                   const int key_lim, const float* lam_s, const uint32_t bar_half) {
-  uint32_t ra[16], rb[16];
+// 2^x for a pair of exponents on the FMA pipe instead of the special-function unit (which, at 16 results per
+// clock and SM, is what bounds this kernel): x = n + f with n = round(x), 2^f on [-0.5, 0.5] by a cubic (maximum
+// relative error 7.5e-5, far below the E2M1 rounding of the result), 2^n by adding n to the exponent field.
+// x must be <= 127; anything below -125 (masked scores are -inf) gives 2^-125, which rounds to code 0.
+__device__ __forceinline__ float2 exp2_fma_pipe(float2 x) {
+  const float2 magic = make_float2(12582912.f, 12582912.f);           // 1.5 * 2^23: the sum's low mantissa bits hold n
+  x.x = fmaxf(x.x, -125.f);
+  x.y = fmaxf(x.y, -125.f);
+  const float2 t = fadd2(x, magic);
+  const float2 n = fadd2(t, make_float2(-12582912.f, -12582912.f));
+  const float2 f = ffma2(n, make_float2(-1.f, -1.f), x);
+  float2 p = ffma2(f, make_float2(0.05517132f, 0.05517132f), make_float2(0.24261055f, 0.24261055f));
+  p = ffma2(p, f, make_float2(0.69326099f, 0.69326099f));
+  p = ffma2(p, f, make_float2(0.99992811f, 0.99992811f));
+  p.x = __uint_as_float(__float_as_uint(p.x) + (__float_as_uint(t.x) << 23));
+  p.y = __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(t.y) << 23));
+  return p;
+}
+
+// How many of the 8 element pairs of every 16-key block take the FMA-pipe exponential (the rest use ex2.approx).
+#ifndef SAGE3_POLY_PAIRS
+#define SAGE3_POLY_PAIRS 0
+#endif
+constexpr int kPolyPairs = SAGE3_POLY_PAIRS;
+
+// P / blockscale = 2^(s*c - (bm*c + log2(1/6))) in [0, 6] -> E2M1 codes into the swizzled P^ tile (64 bytes per
+// row); returns the row sum of the unquantised P = sum over blocks of (sum of P/blockscale) * blockscale
+// (softmax_fused.h:135-153).  neg_e[b] = -(bm_b*c + log2(1/6)), sb[b] = the block's unrounded scale.
+// K-packing mode with slot_first: the first column of every block is the group's mean slot carrying a copy of the
+// first token's score; its P^ goes to the MMA like any other, but it is no token and stays out of the row sum
+// (softmax_fused.h:48-64).
+template <bool kPacked>
+__device__ __forceinline__ float exp_quantise_store(const uint32_t (&s)[128], const float c, const float (&neg_e)[8],
+                                                    const float (&sb)[8], uint8_t* p_row, const int swz,
+                                                    const bool slot_first) {
   const float2 c2 = make_float2(c, c);
   float lsum = 0.f;
   uint32_t code[4];
-  tmem_ld16(tm_S, ra);
-  float2 ns = st[0];
 #pragma unroll
   for (int blk = 0; blk < 8; ++blk) {
-    uint32_t (&r)[16] = (blk & 1) ? rb : ra;
-    uint32_t (&rn)[16] = (blk & 1) ? ra : rb;
-    tmem_wait_ld();
-    if (blk < 7) tmem_ld16(tm_S + (blk + 1) * 16, rn);
-    const float2 ns_next = st[((blk + 1) & 7) * 128];
-    if (kMask) {
-#pragma unroll
-      for (int i = 0; i < 16; ++i) r[i] = (n0 + blk * 16 + i > key_lim) ? 0xff800000u : r[i];
-    }
-    const float2 nb2 = make_float2(ns.x, ns.x);
+    const float2 nb2 = make_float2(neg_e[blk], neg_e[blk]);
     float2 e[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      e[i] = ffma2(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), c2, nb2);
-      e[i].x = ex2_approx(e[i].x);
-      e[i].y = ex2_approx(e[i].y);
+      e[i] = ffma2(make_float2(__uint_as_float(s[16 * blk + 2 * i]), __uint_as_float(s[16 * blk + 2 * i + 1])), c2, nb2);
+      // the pairs that take the FMA pipe are spread over the block (and shifted from block to block) so that both
+      // pipes have work at any time
+      if (((i + blk) & 7) < kPolyPairs) {
+        e[i] = exp2_fma_pipe(e[i]);
+      } else {
+        e[i].x = ex2_approx(e[i].x);
+        e[i].y = ex2_approx(e[i].y);
+      }
     }
     const float2 s4 = fadd2(fadd2(fadd2(e[0], e[1]), fadd2(e[2], e[3])), fadd2(fadd2(e[4], e[5]), fadd2(e[6], e[7])));
-    lsum = fmaf(s4.x + s4.y, ns.y, lsum);
+    float bsum = s4.x + s4.y;
+    if (kPacked && slot_first) bsum -= e[0].x;
+    lsum = fmaf(bsum, sb[blk], lsum);
     code[(blk & 1) * 2 + 0] = f32x8_to_e2m1x8(e[0].x, e[0].y, e[1].x, e[1].y, e[2].x, e[2].y, e[3].x, e[3].y);
     code[(blk & 1) * 2 + 1] = f32x8_to_e2m1x8(e[4].x, e[4].y, e[5].x, e[5].y, e[6].x, e[6].y, e[7].x, e[7].y);
     if (blk & 1) *reinterpret_cast<uint4*>(p_row + (((blk >> 1) ^ swz) << 4)) = make_uint4(code[0], code[1], code[2], code[3]);
-    if (blk == 3) {
-      // keys 0-63 of P^ and their scales are in shared memory: the first half of the P.V MMA can be issued
-      fence_proxy_async_smem();
-      mbar_arrive(bar_half);
-    }
-    ns = ns_next;
   }
-  l = fmaf(l, alpha, lsum);
-}
-
-// Tiles that need the key-padding / causal mask are rare (the last key tile, the diagonal) and go
-// through real calls so that their extra selects do not cost the hot path registers.
-template <bool kPacked>
-__device__ __noinline__ float softmax_pass1_masked(const uint32_t tm_S, const float c, float& m, float2* st,
-                                                   uint2& sfp, const int n0, const int key_lim, const float* lam_s) {
-  return softmax_pass1_impl<true, kPacked>(tm_S, c, m, st, sfp, n0, key_lim, lam_s);
-}
-template <bool kPacked>
-__device__ __noinline__ void softmax_pass2_masked(const uint32_t tm_S, const float c, const float alpha, float& l,
-                                                  const float2* st, uint8_t* p_row, const int swz, const int n0,
-                                                  const int key_lim, const float* lam_s, const uint32_t bar_half) {
-  softmax_pass2_impl<true, kPacked>(tm_S, c, alpha, l, st, p_row, swz, n0, key_lim, lam_s, bar_half);
+  return lsum;
 }
 
 // K-packing mode: 15 tokens occupy 16 key slots (fwd_mainloop.cu:273-303).  Last slot that token `tok` or an
@@ -393,8 +334,10 @@ __device__ __forceinline__ Work get_work(const KParams& P, const int w) {
   k.hkv = k.hq / (P.Hq / P.Hkv);
 #if SAGE3_VARLEN_BUILD
   k.q_base = P.cu_q[k.b];
-  k.Nq = P.cu_q[k.b + 1] - k.q_base;
-  k.Nk = P.cu_k[k.b + 1] - P.cu_k[k.b];
+  // a sequence longer than the caller's max_seqlen is cut there: the operand layouts (and the workspace) are
+  // sized by max_seqlen, so tile indices beyond it must never be formed
+  k.Nq = min(P.cu_q[k.b + 1] - k.q_base, P.Nq);
+  k.Nk = min(P.cu_k[k.b + 1] - P.cu_k[k.b], P.Nk);
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
     const int qt = 2 * k.pair + t;
@@ -456,11 +399,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
     for (int t = 0; t < 2; ++t) {
       mbar_init(bars + Bars::q_full + 8 * t, 1);
       mbar_init(bars + Bars::q_empty + 8 * t, 1);          // tcgen05.commit after the last QK that reads the tile
-      mbar_init(bars + Bars::s_full + 8 * t, 1);
+      mbar_init(bars + Bars::s_full + 8 * t, 1);           // tcgen05.commit
       mbar_init(bars + Bars::p_full + 8 * t, 128);
-      mbar_init(bars + Bars::p_half + 8 * t, 128);
+      mbar_init(bars + Bars::pv_done + 8 * t, 1);          // tcgen05.commit
+      mbar_init(bars + Bars::o_free + 8 * t, 128);
       mbar_init(bars + Bars::epi + 8 * t, 128);
-      mbar_init(bars + Bars::o_full + 8 * t, 1);
     }
     for (int s = 0; s < kStages; ++s) {
       mbar_init(bars + Bars::k_full + 8 * s, 1);
@@ -469,7 +412,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       mbar_init(bars + Bars::v_empty + 8 * s, 1);          // tcgen05.commit
       mbar_init(bars + Bars::ds_ready + 8 * s, 1);
     }
-    mbar_init(bars + Bars::o_free, 128);
+    mbar_init(bars + Bars::s_free, 128);
     mbar_init(bars + Bars::drain, 1);
     mbar_init(bars + Bars::drain + 8, 1);
     // a failure reported by an earlier CTA (or an earlier launch that shares *status) stops new work
@@ -494,8 +437,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(smem + L::bars + Bars::tmem_slot);
-  const uint32_t tm_O = tmem + 256;
-  const uint32_t tm_sfq = tmem + 384, tm_sfk = tmem + 400, tm_sfp = tmem + 408, tm_sfv = tmem + 424;
+  // columns: O0 [0, D)  O1 [D, 2D)  S [2D, 2D + 128)  scale factors behind
+  const uint32_t tm_Sbuf = tmem + 2 * D;
+  const uint32_t tm_sfq = tm_Sbuf + 128, tm_sfk = tm_sfq + 16, tm_sfp = tm_sfk + 8, tm_sfv = tm_sfp + 16;
 
   // read once after the barrier: every warp takes the same branch, so the register hand-over
   // below (setmaxnreg) is always executed by whole warpgroups
@@ -606,7 +550,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         const uint32_t b1_lo = ((sbase + L::b1) >> 4) | (((uint32_t)(L::zero - L::b1) >> 4) << 16);
         bool ok = true;
         uint32_t g = 0;                       // K stages consumed so far
-        uint32_t sq[2] = {0, 0};              // QK groups issued so far per tile slot (= S_t tiles produced)
+        uint32_t nqk = 0;                     // QK groups issued so far (= uses of the score buffer)
         uint32_t qn[2] = {0, 0};              // Q tiles taken so far per slot
         for (int r = 0, w; ok && (w = work_at(r, total_work)) >= 0; ++r) {
           const Work wk = get_work<kCausal, kPacked>(P, w);
@@ -619,9 +563,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
 #pragma unroll
             for (int t = 0; t < 2; ++t) {
               if (!ok || j >= wk.n_t[t]) continue;
-              // S_t must be free: the softmax of the previous tile in this slot (this or the previous work
-              // item) has consumed it and signalled p_full
-              if (sq[t] > 0 && !(ok = wait_bar<kIssuerHint>(bars + Bars::p_full + 8 * t, (sq[t] - 1) & 1, abort_s, P.status, 23))) break;
+              // the one score buffer must be free: the softmax warpgroup that got the previous Q.K^T (the other
+              // query tile, or this one in the previous key tile) has copied it into registers
+              if (nqk > 0 && !(ok = wait_bar<kIssuerHint>(bars + Bars::s_free, (nqk - 1) & 1, abort_s, P.status, 23))) break;
               if (it == wk.n_max - wk.n_t[t]) {                    // first key tile of this query tile
                 if (!(ok = wait_bar<kIssuerHint>(bars + Bars::q_full + 8 * t, qn[t] & 1, abort_s, P.status, 20))) break;
                 ++qn[t];
@@ -635,18 +579,17 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
 #pragma unroll
                 for (int kb = 0; kb < kKB; ++kb) tc_cp_sf(tm_sfk + 4 * kb, sfk_lo + s * 64 + kb * 32, HI_SF);
               }
-              const uint32_t tm_S = tmem + 128 * t;
               if (has_ds) {
                 // buffer i sits i*2048 bytes higher, so its distance to the shared zero chunk is i*2048 smaller
                 const uint32_t i = (uint32_t)(s * 2 + t);
-                tc_mma_bf16(tm_S, a1_lo, HI_SF, b1_lo + i * 128u - ((i * 128u) << 16), HI_SF, idesc_r1, 0);
+                tc_mma_bf16(tm_Sbuf, a1_lo, HI_SF, b1_lo + i * 128u - ((i * 128u) << 16), HI_SF, idesc_r1, 0);
               }
 #pragma unroll
               for (int kb = 0; kb < kKB; ++kb)
-                tc_mma_nvf4(tm_S, q_lo + t * (L::kQBytes >> 4) + kb * 2, HI_QK, k_lo + s * (L::kKBytes >> 4) + kb * 2, HI_QK,
+                tc_mma_nvf4(tm_Sbuf, q_lo + t * (L::kQBytes >> 4) + kb * 2, HI_QK, k_lo + s * (L::kKBytes >> 4) + kb * 2, HI_QK,
                             idesc_qk, tm_sfq + 8 * t + 4 * kb, tm_sfk + 4 * kb, (has_ds || kb > 0) ? 1u : 0u);
               tc_commit(bars + Bars::s_full + 8 * t);
-              ++sq[t];
+              ++nqk;
               if (it == wk.n_max - 1) tc_commit(bars + Bars::q_empty + 8 * t);   // last read of this Q tile
             }
             if (ok) tc_commit(bars + Bars::k_empty + 8 * s);
@@ -659,8 +602,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         }
       } else if (warp == 11 && lane == 0) {
         // ---------------------------------------------------------------- PV issuer
-        // O_tile = P_t V for both tiles, from its own thread so that waiting for the shared product
-        // buffer never delays the next QK.
+        // O_t += P^_t V^ for both tiles, from its own thread so that waiting for P^ never delays the next QK.
+        // The first key tile of a work item overwrites O_t (no accumulate) - once the epilogue of the previous item
+        // in that slot has read it out.
         constexpr uint32_t idesc_pv = make_idesc_nvf4(kBlockM, D);
         constexpr uint32_t HI_PV = (512u >> 4) | (1u << 14) | (4u << 29);
         constexpr uint32_t HI_SF = (128u >> 4) | (1u << 14);
@@ -668,7 +612,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         const uint32_t p_lo = ((sbase + L::p) >> 4) | LBO1, v_lo = ((sbase + L::v) >> 4) | LBO1;
         const uint32_t sfv_lo = (sbase + L::sfv) >> 4, sfp_lo = (sbase + L::sfp) >> 4;
         bool ok = true;
-        uint32_t g = 0, pv_cnt[2] = {0, 0}, pv_total = 0;
+        uint32_t g = 0, pv_cnt[2] = {0, 0}, n_epi[2] = {0, 0};
         for (int r = 0, w; ok && (w = work_at(r, total_work)) >= 0; ++r) {
           const Work wk = get_work<kCausal, kPacked>(P, w);
           for (int it = 0; ok && it < wk.n_max; ++it, ++g) {
@@ -683,21 +627,21 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
             for (int t = 0; t < 2; ++t) {
               const bool act = t == 0 ? (j < wk.n_t[0]) : act1;
               if (!(ok && act)) continue;
-              // first half (keys 0-63) as soon as the softmax has written it, while it still works on the rest
-              if (!(ok = wait_bar<kIssuerHint>(bars + Bars::p_half + 8 * t, pv_cnt[t] & 1, abort_s, P.status, 27))) break;
-              if (pv_total > 0 && !(ok = wait_bar<kIssuerHint>(bars + Bars::o_free, (pv_total - 1) & 1, abort_s, P.status, 22))) break;
-              tc_fence_after();
-              tc_cp_sf(tm_sfp + 8 * t, sfp_lo + t * 64, HI_SF);
-              tc_mma_nvf4(tm_O, p_lo + t * (L::kPBytes >> 4), HI_PV, v_lo + s * (L::kVBytes >> 4), HI_PV, idesc_pv,
-                          tm_sfp + 8 * t, tm_sfv, 0);
+              const bool first_tile = it == wk.n_max - wk.n_t[t];
               if (!(ok = wait_bar<kIssuerHint>(bars + Bars::p_full + 8 * t, pv_cnt[t] & 1, abort_s, P.status, 26))) break;
+              if (first_tile) {
+                if (n_epi[t] > 0 && !(ok = wait_bar<kIssuerHint>(bars + Bars::o_free + 8 * t, (n_epi[t] - 1) & 1, abort_s, P.status, 22))) break;
+                ++n_epi[t];
+              }
               tc_fence_after();
-              tc_cp_sf(tm_sfp + 8 * t + 4, sfp_lo + t * 64 + 32, HI_SF);
-              tc_mma_nvf4(tm_O, p_lo + t * (L::kPBytes >> 4) + 2, HI_PV, v_lo + s * (L::kVBytes >> 4) + 2, HI_PV, idesc_pv,
-                          tm_sfp + 8 * t + 4, tm_sfv + 4, 1);
-              tc_commit(bars + Bars::o_full + 8 * t);
+#pragma unroll
+              for (int kb = 0; kb < 2; ++kb) tc_cp_sf(tm_sfp + 8 * t + 4 * kb, sfp_lo + t * 64 + kb * 32, HI_SF);
+#pragma unroll
+              for (int kb = 0; kb < 2; ++kb)
+                tc_mma_nvf4(tmem + t * D, p_lo + t * (L::kPBytes >> 4) + kb * 2, HI_PV, v_lo + s * (L::kVBytes >> 4) + kb * 2, HI_PV,
+                            idesc_pv, tm_sfp + 8 * t + 4 * kb, tm_sfv + 4 * kb, (first_tile && kb == 0) ? 0u : 1u);
+              tc_commit(bars + Bars::pv_done + 8 * t);
               ++pv_cnt[t];
-              ++pv_total;
               if (t == 1 || !act1) tc_commit(bars + Bars::v_empty + 8 * s);   // last PV of this stage
             }
           }
@@ -708,19 +652,19 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         }
       }
     } else {
-      // ------------------------------------------------------------------ softmax + O accumulation
+      // ------------------------------------------------------------------ softmax
       asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(RegSplit<D>::softmax));
       const int t = warp >> 2;                                   // query tile slot of this warpgroup
       const int row = threadIdx.x & 127;                         // tensor-memory lane
       const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-      const uint32_t tm_S = tmem + 128 * t + lane_addr;
+      const uint32_t tm_S = tm_Sbuf + lane_addr;
+      const uint32_t tm_O = tmem + t * D + lane_addr;
       const float c = P.scale_log2;
       uint8_t* p_row = smem + L::p + t * L::kPBytes + row * 64;
       const int swz = (row >> 1) & 3;
-      float2* st = reinterpret_cast<float2*>(smem + L::stats) + t * 8 * 128 + row;
       uint32_t* sfp_row = reinterpret_cast<uint32_t*>(smem + L::sfp + t * 1024 + sf_atom_offset(row, 0));
       const uint32_t bar_s = bars + Bars::s_full + 8 * t, bar_p = bars + Bars::p_full + 8 * t;
-      const uint32_t bar_o = bars + Bars::o_full + 8 * t, bar_h = bars + Bars::p_half + 8 * t;
+      const uint32_t bar_pv = bars + Bars::pv_done + 8 * t;
       uint32_t sc = 0;                                           // key tiles processed so far by this warpgroup
       uint32_t ne = 0;                                           // epilogue rendezvous so far
       uint32_t g0 = 0;                                           // K/V stages the CTA used before this work item
@@ -742,7 +686,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           // reference's store_zero (fwd_epilogue.cu:150-183); nothing if the tile does not exist
           if (SEQ_TILE_EXISTS && qpos < SEQ_NQ) {
             for (int i = 0; i < D / 8; ++i) reinterpret_cast<uint4*>(orow)[i] = make_uint4(0, 0, 0, 0);
-            if (P.lse) P.lse[((int64_t)wk.b * P.Hq + wk.hq) * P.Nq + qpos] = INFINITY;
+            if (P.lse) P.lse[((int64_t)wk.b * P.Hq + wk.hq) * P.Nq + qpos] = -INFINITY;
           }
           continue;
         }
@@ -755,72 +699,109 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         };
         const int key_lim = min(SEQ_NK - 1, kCausal ? causal_limit(qpos) : 0x7fffffff);
         const int first_row_lim = kCausal ? causal_limit(q0) : 0x7fffffff;
-        float2 O2[D / 2];
-#pragma unroll
-        for (int i = 0; i < D / 2; ++i) O2[i] = make_float2(0.f, 0.f);
-        float m = -INFINITY, l = 0.f;                            // m in raw score units
+        float m_ref = -INFINITY, l = 0.f;                        // reference maximum (raw score units), row sum
 
         for (int it = 0; it < n_mine; ++it, ++sc) {
           const int j = n_mine - 1 - it;
           const int n0 = j * kBlockN;
           const bool need_mask = (n0 + kBlockN - 1 >= SEQ_NK) || (kCausal && n0 + kBlockN - 1 > first_row_lim);
-          const float* lam_s = nullptr;
-          if (kPacked) {
-            // lambda of this key tile arrived with its K stage, i.e. before the Q.K^T MMA whose completion is
-            // awaited next.  Its slot is rewritten 2*kStages key tiles later, which the producer can only do
-            // after the Q.K^T of tile g+kStages is complete - issued after both warpgroups finished tile g.
-            const uint32_t g = g_first + (uint32_t)it;
-            lam_s = reinterpret_cast<const float*>(smem + L::lam) + (g % (2 * kStages)) * 128;
-          }
           if (!(ok = wait_bar<false>(bar_s, sc & 1, abort_s, P.status, 30))) break;
           tc_fence_after();
-          uint2 sfp;
-          const float alpha = need_mask ? softmax_pass1_masked<kPacked>(tm_S, c, m, st, sfp, n0, key_lim, lam_s)
-                                        : softmax_pass1_impl<false, kPacked>(tm_S, c, m, st, sfp, 0, 0, lam_s);
-          sfp_row[0] = sfp.x;
-          sfp_row[128] = sfp.y;
-          if (need_mask) softmax_pass2_masked<kPacked>(tm_S, c, alpha, l, st, p_row, swz, n0, key_lim, lam_s, bar_h);
-          else softmax_pass2_impl<false, kPacked>(tm_S, c, alpha, l, st, p_row, swz, 0, 0, lam_s, bar_h);
-          // S consumed and P^ written: hand both to the MMA issuers
+          uint32_t s[128];
+          load_scores(tm_S, s);
+          // the scores are in registers: the Q.K^T of the other query tile may overwrite the buffer
+          tc_fence_before();
+          mbar_arrive(bars + Bars::s_free);
+          if (kPacked) {
+            // lambda of this key tile arrived with its K stage, i.e. before the Q.K^T MMA whose completion was
+            // awaited above.  Its slot is rewritten 2*kStages key tiles later, which the producer can only do
+            // after the Q.K^T of tile g+kStages is complete - issued after both warpgroups finished tile g.
+            const uint32_t g = g_first + (uint32_t)it;
+            const float* lam_s = reinterpret_cast<const float*>(smem + L::lam) + (g % (2 * kStages)) * 128;
+#pragma unroll
+            for (int blk = 0; blk < 8; ++blk) apply_lambda(&s[16 * blk], lam_s + 16 * blk);
+          }
+          if (need_mask) {
+            const int lim = key_lim - n0;                        // columns beyond it are masked
+#pragma unroll
+            for (int i = 0; i < 128; ++i) s[i] = (i > lim) ? 0xff800000u : s[i];
+          }
+          if (kPacked && P.slot_first) {
+            // the other K-packing variant (fwd_mainloop.cu:847-891): the mean slot carries the (masked) score of the
+            // group's first token - its V row holds that token's FP4 remainder - except, under the causal mask, in
+            // the group of the diagonal token and beyond
+            const int qk = qpos + SEQ_NK_LOG - SEQ_NQ;           // the diagonal key token of this row
+            const int last_group = kCausal ? (qk < 0 ? -1 : qk / 15 - 1) : 0x7ffffff;   // last group whose slot may be used
+#pragma unroll
+            for (int blk = 0; blk < 8; ++blk) {
+              const int col = n0 + 16 * blk;
+              const bool usable = !kCausal || (col < SEQ_NK && (col >> 4) <= last_group);
+              s[16 * blk] = usable ? s[16 * blk + 1] : 0xff800000u;
+            }
+          }
+          float bm[8];
+#pragma unroll
+          for (int blk = 0; blk < 8; ++blk) bm[blk] = max16(&s[16 * blk]);
+          const float m_loc = fmax3(fmax3(bm[0], bm[1], bm[2]), fmax3(bm[3], bm[4], bm[5]), fmaxf(bm[6], bm[7]));
+          if (it == 0) {
+            m_ref = m_loc;                                       // O_t is overwritten by this tile's P.V
+          } else {
+            // (-inf) - (-inf) = NaN compares false: a row that has seen no key yet and sees none now stays put
+            const bool grow = (m_loc - m_ref) * c > kLazyLog2;
+            if (__any_sync(0xffffffffu, grow)) {
+              // O_t *= 2^((m_ref - m_loc) c) for the rows that need it, in place in tensor memory; the P.V of the
+              // previous key tile must have landed first.  Rare: the maximum has to grow by a factor 2^kLazyLog2.
+              if (!(ok = wait_bar<false>(bar_pv, (sc - 1) & 1, abort_s, P.status, 32))) break;
+              tc_fence_after();
+              const float alpha = grow ? ex2_approx((m_ref - m_loc) * c) : 1.0f;
+              if (grow) m_ref = m_loc;
+              l *= alpha;
+              const float2 al2 = make_float2(alpha, alpha);
+#pragma unroll
+              for (int ch = 0; ch < D / 16; ++ch) {
+                uint32_t o[16];
+                tmem_ld16(tm_O + ch * 16, o);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float2 x = ffma2(make_float2(__uint_as_float(o[2 * i]), __uint_as_float(o[2 * i + 1])), al2,
+                                         make_float2(0.f, 0.f));
+                  o[2 * i] = __float_as_uint(x.x); o[2 * i + 1] = __float_as_uint(x.y);
+                }
+                tmem_st16(tm_O + ch * 16, o);
+              }
+              tmem_wait_st();
+            }
+          }
+          const float m_fin = (m_ref == -INFINITY) ? 0.f : m_ref;
+          const float off = fmaf(m_fin, c, kLog2InvTop);          // P = 2^(s*c - off) in (0, 2688]
+          float neg_e[8], sb[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float e = fmaf(bm[i], c, kLog2Inv6);
+            sb[i] = ex2_approx(e - off);
+            neg_e[i] = (bm[i] == -INFINITY) ? 0.f : -e;
+          }
+          // P^ and its scales of the previous key tile must have been consumed by its P.V MMAs
+          if (sc > 0 && !(ok = wait_bar<false>(bar_pv, (sc - 1) & 1, abort_s, P.status, 31))) break;
+          sfp_row[0] = f32x2_to_e4m3x2(sb[0], sb[1]) | (f32x2_to_e4m3x2(sb[2], sb[3]) << 16);     // keys 0-63 of the tile
+          sfp_row[128] = f32x2_to_e4m3x2(sb[4], sb[5]) | (f32x2_to_e4m3x2(sb[6], sb[7]) << 16);   // keys 64-127
+          l += exp_quantise_store<kPacked>(s, c, neg_e, sb, p_row, swz, P.slot_first);
+          // P^ written (and O_t rescaled if it had to be): hand the tile to the PV issuer
           tc_fence_before();
           fence_proxy_async_smem();
           mbar_arrive(bar_p);
-          // While the QK MMA of the next key tile is issued and runs, the P.V product of this one
-          // (issued by the other issuer thread at the same time) is folded into O.  Its completion
-          // also means P^ and its scales may be overwritten by the next iteration.
-          if (!(ok = wait_bar<false>(bar_o, sc & 1, abort_s, P.status, 31))) break;
-          // O = O * alpha + (P^ V^ of this key tile), read from tensor memory 16 columns at a time with the
-          // next load in flight; the shared product buffer is released as soon as it is in registers
-          tc_fence_after();
-          const float2 al2 = make_float2(alpha, alpha);
-          uint32_t ra[16], rb[16];
-          tmem_ld16(tm_O + lane_addr, ra);
-#pragma unroll
-          for (int ch = 0; ch < D / 16; ch += 2) {
-            tmem_wait_ld();
-            tmem_ld16(tm_O + lane_addr + (ch + 1) * 16, rb);
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              O2[ch * 8 + i] = ffma2(O2[ch * 8 + i], al2, make_float2(__uint_as_float(ra[2 * i]), __uint_as_float(ra[2 * i + 1])));
-            tmem_wait_ld();
-            if (ch + 2 < D / 16) {
-              tmem_ld16(tm_O + lane_addr + (ch + 2) * 16, ra);
-            } else {
-              tc_fence_before();
-              mbar_arrive(bars + Bars::o_free);
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              O2[(ch + 1) * 8 + i] = ffma2(O2[(ch + 1) * 8 + i], al2, make_float2(__uint_as_float(rb[2 * i]), __uint_as_float(rb[2 * i + 1])));
-          }
         }
 
         // ---- epilogue: O / l -> bf16 -> global.  D=128, dense batches: through a swizzled staging tile in shared
         // memory and one TMA store per 64 columns - a thread owns a whole output row, so direct stores put 32
-        // different rows into every store instruction; at N = 1K that cost 6 400 cycles per work item and
-        // warpgroup, one and a half key tiles.  D=64 (half the bytes; measured 4 % slower with the staging) and
-        // packed variable-length outputs (a tile must not spill into the next sequence) store directly.
+        // different rows into every store instruction.  D=64 (half the bytes; measured 4 % slower with the staging)
+        // and packed variable-length outputs (a tile must not spill into the next sequence) store directly.
         if (!ok) break;
+        if (!(ok = wait_bar<false>(bar_pv, (sc - 1) & 1, abort_s, P.status, 33))) break;   // the last P.V has landed
+        tc_fence_after();
+        const float inv = (l == 0.f || l != l) ? 0.f : 1.0f / l;
+        const float2 inv2 = make_float2(inv, inv);
         if (kTmaStore) {
           uint8_t* stage = smem + L::ostage + t * (D / 64) * L::kOStage;
           const uint32_t bar_e = bars + Bars::epi + 8 * t;
@@ -829,16 +810,33 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           mbar_arrive(bar_e);
           if (!(ok = wait_bar<false>(bar_e, ne & 1, abort_s, P.status, 35))) break;
           ++ne;
-          const float inv = (l == 0.f || l != l) ? 0.f : 1.0f / l;
+          uint32_t oa[16], ob[16];
+          tmem_ld16(tm_O, oa);
 #pragma unroll
-          for (int i = 0; i < D / 8; ++i) {
-            uint4 o;
-            o.x = pack_bf16(O2[4 * i + 0].x * inv, O2[4 * i + 0].y * inv);
-            o.y = pack_bf16(O2[4 * i + 1].x * inv, O2[4 * i + 1].y * inv);
-            o.z = pack_bf16(O2[4 * i + 2].x * inv, O2[4 * i + 2].y * inv);
-            o.w = pack_bf16(O2[4 * i + 3].x * inv, O2[4 * i + 3].y * inv);
-            *reinterpret_cast<uint4*>(stage + (i >> 3) * L::kOStage + row * 128 + (((i & 7) ^ (row & 7)) << 4)) = o;
+          for (int ch = 0; ch < D / 16; ++ch) {
+            uint32_t (&o)[16] = (ch & 1) ? ob : oa;
+            uint32_t (&on)[16] = (ch & 1) ? oa : ob;
+            tmem_wait_ld();
+            if (ch + 1 < D / 16) tmem_ld16(tm_O + (ch + 1) * 16, on);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint4 v;
+              float2 x;
+              x = ffma2(make_float2(__uint_as_float(o[8 * h + 0]), __uint_as_float(o[8 * h + 1])), inv2, make_float2(0.f, 0.f));
+              v.x = pack_bf16(x.x, x.y);
+              x = ffma2(make_float2(__uint_as_float(o[8 * h + 2]), __uint_as_float(o[8 * h + 3])), inv2, make_float2(0.f, 0.f));
+              v.y = pack_bf16(x.x, x.y);
+              x = ffma2(make_float2(__uint_as_float(o[8 * h + 4]), __uint_as_float(o[8 * h + 5])), inv2, make_float2(0.f, 0.f));
+              v.z = pack_bf16(x.x, x.y);
+              x = ffma2(make_float2(__uint_as_float(o[8 * h + 6]), __uint_as_float(o[8 * h + 7])), inv2, make_float2(0.f, 0.f));
+              v.w = pack_bf16(x.x, x.y);
+              const int i = 2 * ch + h;                          // 16-byte chunk of the 256-byte output row
+              *reinterpret_cast<uint4*>(stage + (i >> 3) * L::kOStage + row * 128 + (((i & 7) ^ (row & 7)) << 4)) = v;
+            }
           }
+          // O_t is in registers / shared memory: the first P.V of the next work item may overwrite it
+          tc_fence_before();
+          mbar_arrive(bars + Bars::o_free + 8 * t);
           fence_proxy_async_smem();
           mbar_arrive(bar_e);
           if (!(ok = wait_bar<false>(bar_e, ne & 1, abort_s, P.status, 36))) break;
@@ -850,23 +848,34 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
                            P.o_token_first ? q0 : wk.hq, P.o_token_first ? wk.hq : q0, wk.b);
             bulk_commit_group();
           }
-        } else if (qpos < SEQ_NQ) {
-          const float inv = (l == 0.f || l != l) ? 0.f : 1.0f / l;
+        } else {
+          const bool live = qpos < SEQ_NQ;
+          uint32_t oa[16], ob[16];
+          tmem_ld16(tm_O, oa);
 #pragma unroll
-          for (int i = 0; i < D / 8; ++i) {
-            uint4 o;
-            o.x = pack_bf16(O2[4 * i + 0].x * inv, O2[4 * i + 0].y * inv);
-            o.y = pack_bf16(O2[4 * i + 1].x * inv, O2[4 * i + 1].y * inv);
-            o.z = pack_bf16(O2[4 * i + 2].x * inv, O2[4 * i + 2].y * inv);
-            o.w = pack_bf16(O2[4 * i + 3].x * inv, O2[4 * i + 3].y * inv);
-            reinterpret_cast<uint4*>(orow)[i] = o;
+          for (int ch = 0; ch < D / 16; ++ch) {
+            uint32_t (&o)[16] = (ch & 1) ? ob : oa;
+            uint32_t (&on)[16] = (ch & 1) ? oa : ob;
+            tmem_wait_ld();
+            if (ch + 1 < D / 16) tmem_ld16(tm_O + (ch + 1) * 16, on);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint4 v;
+              v.x = pack_bf16(__uint_as_float(o[8 * h + 0]) * inv, __uint_as_float(o[8 * h + 1]) * inv);
+              v.y = pack_bf16(__uint_as_float(o[8 * h + 2]) * inv, __uint_as_float(o[8 * h + 3]) * inv);
+              v.z = pack_bf16(__uint_as_float(o[8 * h + 4]) * inv, __uint_as_float(o[8 * h + 5]) * inv);
+              v.w = pack_bf16(__uint_as_float(o[8 * h + 6]) * inv, __uint_as_float(o[8 * h + 7]) * inv);
+              if (live) reinterpret_cast<uint4*>(orow)[2 * ch + h] = v;
+            }
           }
+          tc_fence_before();
+          mbar_arrive(bars + Bars::o_free + 8 * t);
         }
         if (qpos < SEQ_NQ) {
           if (P.lse) {
-            // natural-log sum of exp(sm_scale * s) over the row (l carries the factor 2688)
+            // natural-log sum of exp(sm_scale * s) over the row (l carries the factor 2688 / 2^kLazyLog2)
             P.lse[((int64_t)wk.b * P.Hq + wk.hq) * P.Nq + qpos] =
-                (l == 0.f) ? -INFINITY : (m * c + log2f(l) + kLog2Inv2688) * (1.0f / kLog2e);
+                (l == 0.f) ? -INFINITY : (m_ref * c + log2f(l) + kLog2InvTop) * (1.0f / kLog2e);
           }
         }
       }
@@ -965,18 +974,28 @@ cudaError_t launch(const AttnArgs& a, cudaStream_t stream) {
   P.scale_log2 = a.sm_scale * kLog2e;
   P.o_token_first = o_ndim == 1;
   P.lam = a.k_lambda;
+  P.slot_first = kPacked && a.slot_first != 0;
   // K-packing mode: Nk counts key slots; 16 slots hold 15 tokens, a partial group one slot more than its tokens
   P.Nk_log = kPacked ? (a.Nk / 16) * 15 + (a.Nk % 16 == 0 ? 0 : a.Nk % 16 - 1) : a.Nk;
 #if SAGE3_VARLEN_BUILD
   P.cu_q = a.cu_q; P.cu_k = a.cu_k;
 #endif
   auto kern = attn_fwd_kernel<D, kCausal, kPacked>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total + 1024);
-  if (e != cudaSuccess) return e;
   // persistent CTAs: one per SM (registers and tensor memory allow exactly one), each walks the work list
   int dev = 0, sms = 0;
-  if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
   if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+  // once per device and instantiation: opt in to the shared memory, and make sure the register hand-over inside
+  // the kernel stays within the pool this build of it is launched with (it would block forever otherwise)
+  static unsigned char ready[64] = {};
+  if (dev < 0 || dev >= 64 || !__atomic_load_n(&ready[dev], __ATOMIC_ACQUIRE)) {
+    cudaFuncAttributes fa;
+    if ((e = cudaFuncGetAttributes(&fa, kern)) != cudaSuccess) return e;
+    if (fa.numRegs * kAttnThreads < 256 * RegSplit<D>::softmax + 128 * RegSplit<D>::role) return cudaErrorLaunchOutOfResources;
+    if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total + 1024)) != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) __atomic_store_n(&ready[dev], 1, __ATOMIC_RELEASE);
+  }
   const int64_t work = (int64_t)a.B * a.Hq * ((Tq + 1) / 2);
   const int64_t grid = work < sms ? work : sms;
   kern<<<(unsigned)grid, kAttnThreads, L::total + 1024, stream>>>(tq, tk, tv, to, P);

@@ -21,6 +21,8 @@ inline int check_shape(const sage3_shape& s) {
   if (s.B <= 0 || s.Hq <= 0 || s.Hkv <= 0 || s.Nq <= 0 || s.Nk <= 0) return SAGE3_ERR_ARGUMENT;
   if (s.D != 64 && s.D != 128) return SAGE3_ERR_UNSUPPORTED;
   if (s.Hq % s.Hkv != 0) return SAGE3_ERR_UNSUPPORTED;
+  // (batch, head) pairs index the second grid dimension of the reduction and delta_s kernels
+  if ((int64_t)s.B * s.Hq > 65535) return SAGE3_ERR_UNSUPPORTED;
   // tile indices and TMA row coordinates are 32-bit
   const int64_t Tq = (s.Nq + 127) / 128, Tk = (s.Nk + 127) / 128;
   if ((int64_t)s.B * s.Hq * Tq * 128 >= (1ll << 31) || (int64_t)s.B * s.Hkv * Tk * 128 >= (1ll << 31))
@@ -48,7 +50,7 @@ const char* sage3_status_string(int status) {
   switch (status) {
     case SAGE3_OK: return "ok";
     case SAGE3_ERR_ARGUMENT: return "invalid argument (null pointer, size, stride or alignment)";
-    case SAGE3_ERR_UNSUPPORTED: return "unsupported shape (head_dim must be 64 or 128, Hq a multiple of Hkv)";
+    case SAGE3_ERR_UNSUPPORTED: return "unsupported shape (head_dim must be 64 or 128, Hq a multiple of Hkv, B*Hq <= 65535)";
     case SAGE3_ERR_CUDA: return "CUDA call failed (see sage3_last_cuda_error)";
     case SAGE3_ERR_DEVICE_WAIT: return "a bounded wait inside a kernel gave up";
     case SAGE3_ERR_TOO_LARGE: return "problem exceeds the fixed scratch of sage3_k_mean_static (2048 partial rows / 2048 heads)";
@@ -114,10 +116,12 @@ static int quant_qkv_impl(const sage3_quant_args* a, const int* cu_q, const int*
   const int Tq = (s.Nq + 127) / 128;
   if (a->q.ptr && a->per_block_mean == 0) {
     // mean over the zero-padded length, as the reference pads before taking it (api.py:186,190)
-    if (!a->scratch || a->scratch_bytes < sage3::quant_scratch_bytes(s.B, s.Hq, s.Nq, s.D)) return SAGE3_ERR_ARGUMENT;
+    if (cu_q != nullptr) return SAGE3_ERR_UNSUPPORTED;   // whole-sequence Q mean is not built for packed batches
+    if (!a->scratch || !aligned16(a->scratch) ||
+        a->scratch_bytes < sage3::quant_scratch_bytes(s.B, s.Hq, s.Nq, s.D))
+      return SAGE3_ERR_ARGUMENT;
     cudaError_t e = sage3::launch_channel_mean(a->q.ptr, a->q.stride_b, a->q.stride_h, a->q.stride_n, s.B, s.Hq, s.Nq,
                                                s.D, (float)(Tq * 128), a->scratch, a->qm, stream);
-    if (cu_q != nullptr) return SAGE3_ERR_UNSUPPORTED;   // whole-sequence Q mean is not built for packed batches
     if (e != cudaSuccess) return cuda_fail(e);
   }
 
@@ -151,7 +155,8 @@ static int quant_qkv_impl(const sage3_quant_args* a, const int* cu_q, const int*
 
 int sage3_quant_qkv(const sage3_quant_args* a, void* stream) { return quant_qkv_impl(a, nullptr, nullptr, stream); }
 
-static int attn_fwd_impl(const sage3_attn_args* a, const float* k_lambda, const int* cu_q, const int* cu_k, void* stream_) {
+static int attn_fwd_impl(const sage3_attn_args* a, const float* k_lambda, const int* cu_q, const int* cu_k, void* stream_,
+                         int slot_first = 0) {
   if (a == nullptr) return SAGE3_ERR_ARGUMENT;
   if (int st = check_shape(a->shape)) return st;
   if (!a->q_codes || !a->q_sf || !a->k_codes || !a->k_sf || !a->vt_codes || !a->vt_sf || !a->out || !a->device_status)
@@ -163,6 +168,7 @@ static int attn_fwd_impl(const sage3_attn_args* a, const float* k_lambda, const 
   const sage3_shape& s = a->shape;
   const int Tq = (s.Nq + 127) / 128;
   if (a->delta_s && a->delta_s_rows != 1 && a->delta_s_rows != Tq) return SAGE3_ERR_ARGUMENT;
+  if (!(a->sm_scale > 0.f)) return SAGE3_ERR_ARGUMENT;          // the row maximum is tracked in raw score units
   cudaStream_t stream = (cudaStream_t)stream_;
   cudaError_t e = cudaMemsetAsync(a->device_status, 0, sizeof(int32_t), stream);
   if (e != cudaSuccess) return cuda_fail(e);
@@ -174,6 +180,7 @@ static int attn_fwd_impl(const sage3_attn_args* a, const float* k_lambda, const 
   k.B = s.B; k.Hq = s.Hq; k.Hkv = s.Hkv; k.Nq = s.Nq; k.Nk = s.Nk; k.D = s.D;
   k.sm_scale = a->sm_scale; k.causal = a->is_causal;
   k.k_lambda = k_lambda;
+  k.slot_first = slot_first;
   k.cu_q = cu_q; k.cu_k = cu_k;
   e = (cu_q != nullptr || cu_k != nullptr) ? sage3::launch_attn_fwd_varlen(k, stream) : sage3::launch_attn_fwd(k, stream);
   if (e != cudaSuccess) return cuda_fail(e);
@@ -182,9 +189,9 @@ static int attn_fwd_impl(const sage3_attn_args* a, const float* k_lambda, const 
 
 int sage3_attn_fwd(const sage3_attn_args* a, void* stream) { return attn_fwd_impl(a, nullptr, nullptr, nullptr, stream); }
 
-int sage3_attn_fwd_packed(const sage3_attn_args* a, const float* k_lambda, void* stream) {
+int sage3_attn_fwd_packed(const sage3_attn_args* a, const float* k_lambda, int32_t mean_slot_first, void* stream) {
   if (k_lambda == nullptr || !aligned16(k_lambda)) return SAGE3_ERR_ARGUMENT;
-  return attn_fwd_impl(a, k_lambda, nullptr, nullptr, stream);
+  return attn_fwd_impl(a, k_lambda, nullptr, nullptr, stream, mean_slot_first != 0);
 }
 
 int sage3_packed_rows(int nk) { return nk <= 0 ? 0 : 16 * ((nk + 14) / 15); }
@@ -196,6 +203,7 @@ int sage3_pack_kv(const sage3_pack_args* a, void* stream_) {
   const sage3_shape& s = a->shape;
   if (s.B <= 0 || s.Hkv <= 0 || s.Nk <= 0) return SAGE3_ERR_ARGUMENT;
   if (s.D != 64 && s.D != 128) return SAGE3_ERR_UNSUPPORTED;
+  if ((int64_t)s.B * s.Hkv > 65535) return SAGE3_ERR_UNSUPPORTED;
   if (int st = check_tensor(a->k)) return st;
   if (int st = check_tensor(a->v)) return st;
   if (a->v.ptr && !a->v_packed) return SAGE3_ERR_ARGUMENT;
@@ -219,6 +227,7 @@ int sage3_pack_kv(const sage3_pack_args* a, void* stream_) {
   p.v = a->v.ptr; p.v_sb = a->v.stride_b; p.v_sh = a->v.stride_h; p.v_sn = a->v.stride_n;
   p.km = km; p.kp = a->k_packed; p.vp = a->v.ptr ? a->v_packed : nullptr; p.lam = a->k_lambda;
   p.B = s.B; p.Hkv = s.Hkv; p.Nk = s.Nk; p.D = s.D;
+  p.split_first = a->split_first != 0;
   cudaError_t e = sage3::launch_pack_kv(p, stream);
   if (e != cudaSuccess) return cuda_fail(e);
   return SAGE3_OK;
@@ -246,6 +255,11 @@ int sage3_attention(const sage3_fwd_args* a, void* stream) {
   if (a->device_status) status = a->device_status;
   const float sm_scale = a->sm_scale > 0.f ? a->sm_scale : 1.0f / sqrtf((float)a->shape.D);
   q.delta_s = a->per_block_mean >= 0 ? ds : nullptr;
+  if (a->km_out && !a->smooth_k) {
+    // no mean is removed: the caller's LSE correction term must vanish
+    cudaError_t e = cudaMemsetAsync(a->km_out, 0, z.km, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e);
+  }
   if (int st = sage3_quant_qkv(&q, stream)) return st;
   sage3_attn_args t{};
   t.shape = a->shape;
@@ -304,6 +318,43 @@ int sage3_k_mean_static(const sage3_shape* shape, const sage3_tensor* k, void* k
                                                     shape->Nk, shape->D, (float)shape->Nk, km_out, (cudaStream_t)stream,
                                                     &too_large);
   if (too_large) return SAGE3_ERR_TOO_LARGE;
+  if (e != cudaSuccess) return cuda_fail(e);
+  return SAGE3_OK;
+}
+
+int sage3_fp4_mma_peak(int n_cols, int bursts, int launches, int32_t* device_status, void* stream_, double* tflops_out) {
+  if ((n_cols != 128 && n_cols != 256) || bursts <= 0 || bursts > (1 << 16) || launches <= 0 || launches > 1024 ||
+      device_status == nullptr || tflops_out == nullptr)
+    return SAGE3_ERR_ARGUMENT;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  cudaError_t e = cudaMemsetAsync(device_status, 0, sizeof(int32_t), stream);
+  if (e != cudaSuccess) return cuda_fail(e);
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  if ((e = cudaEventCreate(&e0)) != cudaSuccess) return cuda_fail(e);
+  if ((e = cudaEventCreate(&e1)) != cudaSuccess) { cudaEventDestroy(e0); return cuda_fail(e); }
+  int ctas = 0;
+  e = sage3::launch_fp4_mma_peak(n_cols, bursts, device_status, stream, &ctas);          // warm-up
+  if (e == cudaSuccess) e = cudaEventRecord(e0, stream);
+  for (int i = 0; e == cudaSuccess && i < launches; ++i)
+    e = sage3::launch_fp4_mma_peak(n_cols, bursts, device_status, stream, &ctas);
+  if (e == cudaSuccess) e = cudaEventRecord(e1, stream);
+  if (e == cudaSuccess) e = cudaEventSynchronize(e1);
+  float ms = 0.f;
+  if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  if (e != cudaSuccess) return cuda_fail(e);
+  const double flops = 2.0 * 128.0 * n_cols * 64.0 * 64.0 * bursts * (double)ctas * launches;
+  *tflops_out = ms > 0.f ? flops / (ms * 1e-3) / 1e12 : 0.0;
+  return sage3_read_device_status(device_status, stream_, nullptr);
+}
+
+int sage3_selftest_bounded_wait(int32_t* device_status, void* stream_) {
+  if (device_status == nullptr) return SAGE3_ERR_ARGUMENT;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  cudaError_t e = cudaMemsetAsync(device_status, 0, sizeof(int32_t), stream);
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = sage3::launch_bounded_wait_selftest(device_status, 77, stream);
   if (e != cudaSuccess) return cuda_fail(e);
   return SAGE3_OK;
 }

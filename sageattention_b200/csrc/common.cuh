@@ -156,6 +156,22 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
   return false;
 }
 
+// Bounded wait on an mbarrier phase used by the kernels' roles; also gives up as soon as any CTA has reported a
+// failure through *status.  A failing poll parks the thread for about 1.5 us (kHinted: about 4 us), so the default
+// limit of 2^21 polls is 3 to 8 seconds; which flavour is faster was measured per role: the shorter park costs
+// issue slots but reacts sooner.  On giving up it raises the CTA's abort flag, records `code` in *status (first
+// writer wins) and returns false - the caller then unwinds instead of hanging the SM.
+template <bool kHinted, uint32_t kPolls = (1u << 21)>
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_s, int* status, int code) {
+  for (uint32_t i = 0; i < kPolls; ++i) {
+    if (mbar_try_wait<kHinted ? 20000 : 0>(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && (*abort_s != 0 || *reinterpret_cast<volatile int*>(status) != 0)) break;
+  }
+  *abort_s = 1;
+  atomicCAS(status, 0, code);
+  return false;
+}
+
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(256, 3) delta_s_kernel(
       mean[4] = bf16_lo(m.z); mean[5] = bf16_hi(m.z); mean[6] = bf16_lo(m.w); mean[7] = bf16_hi(m.w);
     }
     // variable-length batch: sequence b starts at token cu_k[b] of the packed tensor and has its own length
-    if (cu_k != nullptr) Nk = cu_k[b + 1] - cu_k[b];
+    if (cu_k != nullptr) Nk = min(cu_k[b + 1] - cu_k[b], Nk);   // cut at max_seqlen like every other kernel
     const __nv_bfloat16* src = k + (cu_k ? (int64_t)cu_k[b] * k_sn : b * k_sb) + hkv * k_sh + c * 8;
     uint4 w[128 / RPP];
 #pragma unroll
@@ -126,8 +126,10 @@ cudaError_t launch_delta_s(const DeltaSArgs& a, cudaStream_t stream) {
   dim3 grid(Tk, a.B * a.Hkv);
   const int smem = (128 * (a.D + 8) + 8 * 16 * 136) * 2;
   // per device and cheap, so set on every call rather than cached per process
-  cudaFuncSetAttribute(delta_s_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (128 * 136 + 8 * 16 * 136) * 2);
-  cudaFuncSetAttribute(delta_s_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (128 * 72 + 8 * 16 * 136) * 2);
+  cudaError_t e = a.D == 128
+      ? cudaFuncSetAttribute(delta_s_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
+      : cudaFuncSetAttribute(delta_s_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
   if (a.D == 128)
     delta_s_kernel<128><<<grid, 256, smem, stream>>>((const __nv_bfloat16*)a.qm, (const __nv_bfloat16*)a.k, a.k_sb, a.k_sh,
                                                   a.k_sn, (const __nv_bfloat16*)a.km, (__nv_bfloat16*)a.ds, a.Hq, a.Hkv,

@@ -37,6 +37,7 @@ struct PackArgs {
   void *kp, *vp;                          // bf16 [B,Hkv,16*G,D] contiguous, G = ceil(Nk/15); vp may be null
   float* lam;                             // fp32 [B,Hkv,ceil(16*G/128)*128]
   int B, Hkv, Nk, D;
+  int split_first = 0;                    // V layout of the reference's v_trick (see pack.cu)
 };
 cudaError_t launch_pack_kv(const PackArgs& a, cudaStream_t stream);
 
@@ -63,10 +64,17 @@ struct AttnArgs {
   float sm_scale;
   int causal;
   const float* k_lambda;                  // K-packing mode: fp32 [B,Hkv,Tk*128]; Nk is then the packed length
+  int slot_first = 0;                     // K-packing mode: mean slot = first token's score (else masked)
   const int* cu_q = nullptr;              // variable-length batches, see QuantArgs; out is then [tokens, Hq, D]
   const int* cu_k = nullptr;
 };
 cudaError_t launch_attn_fwd(const AttnArgs& a, cudaStream_t stream);
 cudaError_t launch_attn_fwd_varlen(const AttnArgs& a, cudaStream_t stream);   // cu_q / cu_k given
+
+// Back-to-back block-scaled FP4 MMAs on resident operands, one CTA per SM (peak.cu); *ctas = CTAs launched.
+cudaError_t launch_fp4_mma_peak(int n_cols, int bursts, int* status, cudaStream_t stream, int* ctas);
+
+// One CTA runs a bounded wait that must give up (selftest.cu); *status receives `code`.
+cudaError_t launch_bounded_wait_selftest(int* status, int code, cudaStream_t stream);
 
 }  // namespace sage3

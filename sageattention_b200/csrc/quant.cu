@@ -51,7 +51,7 @@ __global__ void __launch_bounds__(kThreads) channel_mean_kernel(
   const int t = threadIdx.x, c = t % CH, rl = t / CH;
   // variable-length batch: sequence b starts at token cu[b] of the packed tensor and has its own length
   if (cu != nullptr) {
-    N = cu[b + 1] - cu[b];
+    N = min(cu[b + 1] - cu[b], N);         // never beyond the caller's max_seqlen (the grid covers no more)
     divisor = (float)max(N, 1);
   }
   const __nv_bfloat16* base = x + (cu ? (int64_t)cu[b] * sn : b * sb) + h * sh + c * 8;
@@ -166,7 +166,7 @@ __global__ void __launch_bounds__(kThreads) quant_qkv_kernel(const QuantLaunch P
     const int* cu = is_q ? P.cu_q : P.cu_k;
     const __nv_bfloat16* src = is_q ? P.q + b * P.q_sb + h * P.q_sh : P.k + b * P.k_sb + h * P.k_sh;
     if (cu != nullptr) {                   // sequence b of a packed [tokens, H, D] tensor
-      N = cu[b + 1] - cu[b];
+      N = min(cu[b + 1] - cu[b], N);       // cut at max_seqlen, which sizes the output layouts
       src = (is_q ? P.q + h * P.q_sh : P.k + h * P.k_sh) + (int64_t)cu[b] * sn;
     }
     uint4 w[NP];
@@ -274,7 +274,7 @@ __global__ void __launch_bounds__(kThreads) quant_qkv_kernel(const QuantLaunch P
     const int c4 = (warp % WPT) * 4 + (lane >> 3);        // group of 4 channels
     const int blk = lane & 7;                              // 16-token block
     const __nv_bfloat16* src = P.v + (P.cu_k ? (int64_t)P.cu_k[b] * P.v_sn : b * P.v_sb) + h * P.v_sh + c4 * 4;
-    const int Nv = P.cu_k ? P.cu_k[b + 1] - P.cu_k[b] : P.Nk;
+    const int Nv = P.cu_k ? min(P.cu_k[b + 1] - P.cu_k[b], P.Nk) : P.Nk;
     uint2 x[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {

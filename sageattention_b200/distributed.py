@@ -96,14 +96,32 @@ def _head_to_seq(x: torch.Tensor, world: int, group, async_op: bool = False):
     return work, finish
 
 
-def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group=None, head_chunks: int = 1,
-                      attn_fn: Optional[Callable] = None, **kwargs) -> torch.Tensor:
+def _chunk_sizes(heads_per_rank: int, head_chunks) -> List[int]:
+    """Heads per rank of every chunk: an int splits evenly, a sequence is taken as it is."""
+    if isinstance(head_chunks, int):
+        if head_chunks < 1 or heads_per_rank % head_chunks != 0:
+            raise ValueError(f"heads per rank ({heads_per_rank}) must be a multiple of head_chunks ({head_chunks})")
+        return [heads_per_rank // head_chunks] * head_chunks
+    sizes = [int(n) for n in head_chunks]
+    if any(n < 1 for n in sizes) or sum(sizes) != heads_per_rank:
+        raise ValueError(f"head chunk sizes {sizes} must be positive and add up to the heads per rank ({heads_per_rank})")
+    return sizes
+
+
+def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group=None, head_chunks=1,
+                      attn_fn: Optional[Callable] = None, exposed: Optional[list] = None, **kwargs) -> torch.Tensor:
     """Sequence-parallel attention.  q, k, v: this rank's sequence shard ``[B, N/P, H, D]`` ("NHD";
     shard r holds tokens ``r*N/P ... (r+1)*N/P - 1``).  Returns the output shard ``[B, N/P, H, D]``.
 
-    Requires ``H % (P * head_chunks) == 0`` and the same head count for q, k, v (expand GQA first).
-    With ``head_chunks > 1`` the all-to-all of the next chunk of heads is in flight while the current
-    chunk is attended.
+    Requires ``H % P == 0`` and the same head count for q, k, v (expand GQA first).  ``head_chunks``: the
+    heads are exchanged and attended in chunks - an int for equal chunks, or a sequence of heads per rank
+    per chunk, e.g. ``[1, 2, 2]`` for 5 heads per rank - so that the all-to-all of the next chunk and the
+    return all-to-all of the previous one are in flight while the current chunk is attended; only the
+    first exchange and the last return are exposed, so small first and last chunks expose the least.
+    Chunk ``c`` with ``n_c`` heads per rank carries the global heads ``[P*o_c, P*(o_c + n_c))`` (``o_c`` = heads
+    per rank of the chunks before it), rank ``p`` attending ``[P*o_c + p*n_c, P*o_c + (p+1)*n_c)``.
+    ``exposed``: a list that receives ``(start, end)`` CUDA event pairs around every point where the compute
+    stream waits for a collective (their elapsed times add up to the exposed communication time).
     """
     if attn_fn is None:
         from .api import sageattn as attn_fn
@@ -111,34 +129,42 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group=N
     B, n, H, D = q.shape
     if k.shape != q.shape or v.shape != q.shape:
         raise ValueError("ulysses_attention expects q, k, v of identical shape [B, N/P, H, D]")
-    if H % (world * head_chunks) != 0:
-        raise ValueError(f"the head count {H} must be a multiple of world_size * head_chunks = {world * head_chunks}")
-    hc = H // head_chunks
-    outs = [None] * head_chunks
+    if H % world != 0:
+        raise ValueError(f"the head count {H} must be a multiple of the world size {world}")
+    sizes = _chunk_sizes(H // world, head_chunks)
+    starts = [world * sum(sizes[:c]) for c in range(len(sizes))]
+
+    def waited(work):
+        if exposed is not None and q.is_cuda:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            work.wait()
+            e1.record()
+            exposed.append((e0, e1))
+        else:
+            work.wait()
 
     def launch(c):
-        sl = slice(c * hc, (c + 1) * hc)
+        sl = slice(starts[c], starts[c] + world * sizes[c])
         return [_seq_to_head(t[:, :, sl], world, group, async_op=True) for t in (q, k, v)]
 
     pending = launch(0)
     back = []
-    for c in range(head_chunks):
+    for c in range(len(sizes)):
         cur = pending
-        if c + 1 < head_chunks:
+        if c + 1 < len(sizes):
             pending = launch(c + 1)
         full = []
         for work, finish in cur:
-            work.wait()
+            waited(work)
             full.append(finish())
-        o = attn_fn(full[0], full[1], full[2], tensor_layout="NHD", **kwargs)          # [B, N, hc/P, D]
+        o = attn_fn(full[0], full[1], full[2], tensor_layout="NHD", **kwargs)          # [B, N, n_c, D]
         back.append(_head_to_seq(o, world, group, async_op=True))
-    for c, (work, finish) in enumerate(back):
-        work.wait()
-        outs[c] = finish()                                                             # [B, n, hc, D] heads in rank order
-    if head_chunks == 1:
-        return outs[0]
-    # chunk c carried global heads [c*hc, (c+1)*hc): rank p's part of it sits at [p*hc/P, (p+1)*hc/P)
-    return torch.cat(outs, dim=2)
+    outs = []
+    for work, finish in back:
+        waited(work)
+        outs.append(finish())                                                          # [B, n, P*n_c, D] heads in rank order
+    return outs[0] if len(outs) == 1 else torch.cat(outs, dim=2)
 
 
 def merge_partial(out_a: torch.Tensor, lse_a: torch.Tensor, out_b: torch.Tensor, lse_b: torch.Tensor):

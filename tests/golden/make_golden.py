@@ -106,6 +106,10 @@ def main(ref_root: str):
         pk[f"{tag}_q"], pk[f"{tag}_k"], pk[f"{tag}_v"] = bits(q), bits(k), bits(v)
         pk[f"{tag}_kp"], pk[f"{tag}_vp"] = bits(kp), bits(vp)
         pk[f"{tag}_lam"], pk[f"{tag}_ds"] = lam.float().numpy(), ds.float().numpy()
+        # the other kernel variant: whole-sequence Q mean and the split-first V layout (v_trick defaults to True)
+        qp0, kp0, vp0, ds0, lam0 = pre(q.clone(), k.clone(), v.clone(), False, 16, None)
+        pk[f"{tag}_qs0"], pk[f"{tag}_vp0"], pk[f"{tag}_ds0"] = bits(qp0), bits(vp0), ds0.float().numpy()
+        assert torch.equal(kp0, kp) and torch.equal(lam0, lam)      # the K side does not depend on the variant
     np.savez_compressed(HERE / "pack_emulation.npz", **pk)
     print("pack_emulation.npz", {k_: v_.shape for k_, v_ in pk.items()})
     np.savez_compressed(HERE / "llama_fixture_qkv.npz", **out)

@@ -222,3 +222,51 @@ def test_operator_can_be_captured_in_a_cuda_graph():
     g.replay()
     torch.cuda.synchronize()
     assert torch.equal(out, sa.sageattn(q2, k2, v2, is_causal=True))
+
+
+def test_bounded_wait_gives_up_and_reports():
+    """A wait on a barrier nothing completes runs out after its (short) poll limit: the kernel returns normally, the
+    status word carries its code, the host call maps it to SAGE3_ERR_DEVICE_WAIT and the context stays usable."""
+    import ctypes as C
+    from sageattention_b200 import _lib
+    lib = _lib.load()
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.sage3_selftest_bounded_wait(st.data_ptr(), stream) == _lib.OK
+    code = C.c_int32(0)
+    assert lib.sage3_read_device_status(st.data_ptr(), stream, C.byref(code)) == _lib.ERR_DEVICE_WAIT
+    assert code.value == 77
+    # the device is still fine: a real operator call right after it succeeds
+    q, k, v = U.make_qkv(1, 2, 2, 256, 256, 128, seed=1, device=DEV)
+    out = sa.sageattn(q, k, v, check_status=True)
+    assert torch.isfinite(out).all()
+
+
+def test_varlen_sequences_longer_than_max_seqlen_are_cut_not_overrun():
+    """A caller that passes max_seqlen smaller than its longest sequence gets that sequence cut at max_seqlen (the
+    operand layouts and the workspace are sized by it): no tile index beyond the layouts is ever formed."""
+    Hq, Hkv, D = 2, 2, 128
+    lens = [300, 700, 128]
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(sum(lens), Hq, D, generator=g).to(torch.bfloat16).to(DEV)
+    k = torch.randn(sum(lens), Hkv, D, generator=g).to(torch.bfloat16).to(DEV)
+    v = torch.randn(sum(lens), Hkv, D, generator=g).to(torch.bfloat16).to(DEV)
+    cu = torch.tensor([0] + np.cumsum(lens).tolist(), dtype=torch.int32, device=DEV)
+    cap = 384
+    out = sa.sageattn_varlen(q, k, v, cu, cu, cap, cap, is_causal=False, check_status=True)
+    for i, n in enumerate(lens):
+        s0 = int(cu[i])
+        m = min(n, cap)
+        one = sa.sageattn(q[s0:s0 + m][None], k[s0:s0 + m][None], v[s0:s0 + m][None], tensor_layout="NHD")[0]
+        cos, l1 = sage3.accuracy(out[s0:s0 + m].float().cpu(), one.float().cpu())
+        assert cos >= 0.9995 and l1 <= 2e-2, (i, cos, l1)
+
+
+def test_host_tensor_entry_point_batched_is_copy_bound_not_stride_bound():
+    """B > 1: the head groups of a [B,H,N,D] host tensor are not contiguous across the batch; the entry point copies
+    them batch entry by batch entry.  Same values as the device operator."""
+    q, k, v = U.make_qkv(3, 8, 4, 500, 500, 128, seed=13)
+    want = sa.sageattn(q.cuda(), k.cuda(), v.cuda(), is_causal=False).cpu()
+    got = sa.sageattn_from_host(q.pin_memory(), k.pin_memory(), v.pin_memory(), head_chunks=4)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)

@@ -105,3 +105,43 @@ def test_k_packing_matches_reference_preprocessing(tag):
     np.testing.assert_allclose(ds.numpy(), z[f"{tag}_ds"], rtol=1e-6, atol=1e-6)
     for n in (0, 1, 14, 15, 16, 29, 30, 100, 32760):
         assert sage3.packed_len_to_logical(sage3.logical_to_packed_len(n)) == n
+    # the other kernel variant (per_block_mean=False): whole-sequence Q mean, split-first V, one delta_s row
+    vp0 = sage3.pad_tokens(sage3.pack_v(v, split_first=True))
+    assert torch.equal(vp0, bf("vp0"))
+    q_pad = sage3.pad_tokens(q)
+    qm0 = q_pad.mean(dim=-2, keepdim=True)
+    assert torch.equal(q_pad - qm0, bf("qs0"))
+    ds0 = torch.matmul(qm0, kp.transpose(-2, -1)).float()
+    np.testing.assert_allclose(ds0.numpy(), z[f"{tag}_ds0"], rtol=1e-6, atol=1e-6)
+
+
+def test_sampled_query_tiles_equal_the_full_evaluation():
+    """attention_quantised(q_tiles=...) - used to check a few tiles of a benchmark-sized problem - gives exactly the
+    rows of the full evaluation."""
+    torch.manual_seed(0)
+    B, H, N, D = 1, 2, 512, 64
+    q, k, v = (torch.randn(B, H, N, D).to(torch.bfloat16) for _ in range(3))
+    qs, ks, vp, ds, _ = sage3.preprocess(q, k, v)
+    qd = sage3.dequant(*sage3.quant_rows(qs)); kd = sage3.dequant(*sage3.quant_rows(ks))
+    vtd = sage3.dequant(*sage3.quant_v_transposed(vp))
+    for causal in (False, True):
+        full, lse = sage3.attention_quantised(qd, kd, vtd, ds, 500, 500, D ** -0.5, causal, True)
+        tiles = [1, 3]
+        qsel = torch.cat([qd[:, :, t * 128:(t + 1) * 128] for t in tiles], 2)
+        part, lp = sage3.attention_quantised(qsel, kd, vtd, ds[:, :, tiles], 500, 500, D ** -0.5, causal, True, q_tiles=tiles)
+        assert torch.equal(part[:, :, :128], full[:, :, 128:256]) and torch.equal(part[:, :, 128:244], full[:, :, 384:500])
+        assert torch.equal(lp[:, :, :128], lse[:, :, 128:256])
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_k_packing_variants_agree_with_fp32_attention(causal):
+    """Both K-packing kernel variants of the restatement (masked mean slot / mean slot takes the first score with the
+    split-first V layout) stay within the reference test's thresholds of fp32 attention on the reference's fixture."""
+    z = np.load(G / "llama_fixture_qkv.npz")
+    q, k, v = (torch.from_numpy(f32(z[f"s256_{n}"])).to(torch.bfloat16) for n in "qkv")
+    ref = sage3.sdpa_fp32(q, k, v, is_causal=causal)
+    for pbm in (True, False):
+        out = sage3.sageattn4_emulated(q, k, v, is_causal=causal, per_block_mean=pbm).float()
+        cos = torch.nn.functional.cosine_similarity(out, ref, dim=-1).mean().item()
+        l1 = torch.nn.functional.l1_loss(out, ref).item()
+        assert 1 - cos < 0.01 and l1 < 0.01, (pbm, cos, l1)

@@ -39,7 +39,7 @@ def test_pack_kernel_matches_oracle(B, H, N, D):
     assert int(diff.max()) <= 1 and float((diff > 0).float().mean()) <= 5e-3
 
 
-def oracle_on_packed_operands(z, sm_scale, causal):
+def oracle_on_packed_operands(z, sm_scale, causal, mean_slot="mask"):
     B, Hq, Hkv, Nq, Nk, D = z.shape
     qc, qs = U.unpack_rows(z.q_codes, z.q_sf)
     kc, ks = U.unpack_rows(z.k_codes, z.k_sf)
@@ -48,7 +48,10 @@ def oracle_on_packed_operands(z, sm_scale, causal):
     kd = torch.from_numpy(nvfp4.dequantize_nvfp4(kc, ks))
     vtd = torch.from_numpy(nvfp4.dequantize_nvfp4(vc, vs))
     ds = z.delta_s.float().cpu()
-    return sage3.attention_quantised(qd, kd, vtd, ds, Nq, z.nk_slots, sm_scale, causal, lamb=z.k_lambda.cpu())
+    if z.delta_s_rows == 1:
+        ds = ds.expand(-1, -1, qd.shape[2] // 128, -1)
+    return sage3.attention_quantised(qd, kd, vtd, ds, Nq, z.nk_slots, sm_scale, causal, lamb=z.k_lambda.cpu(),
+                                     mean_slot=mean_slot)
 
 
 CASES = [
@@ -98,10 +101,46 @@ def test_packed_operator_matches_emulation(layout, causal):
 
 def test_packed_mode_rejects_unsupported_variants():
     q, k, v = U.make_qkv(1, 2, 2, 64, 64, 128, seed=1, device=DEV)
-    with pytest.raises(NotImplementedError):
-        sa.sageattn4_blackwell(q, k, v, per_block_mean=False)
     with pytest.raises(AssertionError):
         sa.sageattn4_blackwell(q, k, v, quant_block=8)
+
+
+@pytest.mark.parametrize("B,H,N,D", [(1, 2, 100, 64), (2, 3, 333, 128), (1, 1, 16, 64), (1, 2, 2000, 128)])
+def test_split_first_v_layout_matches_oracle(B, H, N, D):
+    """The V layout of the reference's v_trick (api.py:158-170): bit-exact against the restatement, which is pinned
+    to the reference's own preprocess_qkv by tests/golden/pack_emulation.npz."""
+    _, k, v = U.make_qkv(B, H, H, 8, N, D, seed=N + D, device=DEV)
+    _, vp, _, _ = sa.pack_kv(k, v, split_first=True)
+    assert torch.equal(vp.cpu(), sage3.pack_v(v.cpu(), split_first=True))
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Nq,Nk,D,causal", CASES)
+def test_mean_slot_first_kernel_matches_oracle_on_same_operands(B, Hq, Hkv, Nq, Nk, D, causal):
+    """The kernel variant the reference builds for per_block_mean=False (fwd_mainloop.cu:847-891): whole-sequence Q
+    mean (one delta_s row), split-first V, the mean slot takes the first token's score and stays out of the row sum."""
+    q, k, v = U.make_qkv(B, Hq, Hkv, Nq, Nk, D, seed=Nq + Nk + D + 2, device=DEV)
+    kp, vp, lam, _ = sa.pack_kv(k, v, split_first=True)
+    z = sa.quantize_qkv(q, kp, vp, per_block_mean=False, smooth_k=False)
+    z.k_lambda, z.nk_slots, z.mean_slot_first = lam, sage3.logical_to_packed_len(Nk), True
+    out = sa.fp4_attention(z, is_causal=causal, check_status=True)
+    ref = oracle_on_packed_operands(z, D ** -0.5, causal, mean_slot="first")
+    cos, l1 = sage3.accuracy(out.float().cpu(), ref)
+    assert cos >= COS_MIN and l1 <= REL_L1_MAX, (cos, l1)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_packed_operator_whole_sequence_mean_variant_matches_emulation(causal):
+    B, Hq, Hkv, N, D = 1, 4, 2, 700, 128
+    q, k, v = U.make_qkv(B, Hq, Hkv, N, N, D, seed=12, device=DEV)
+    out = sa.sageattn4_blackwell(q, k, v, is_causal=causal, per_block_mean=False, check_status=True)
+    emu = sage3.sageattn4_emulated(q.cpu(), k.cpu(), v.cpu(), is_causal=causal, per_block_mean=False)
+    cos, l1 = sage3.accuracy(out.float().cpu(), emu.float())
+    assert cos >= COS_MIN and l1 <= REL_L1_MAX, (cos, l1)
+    # the two V layouts are interchangeable for the masked-slot kernel (the slot's V row is never used there)
+    out2 = sa.sageattn4_blackwell(q, k, v, is_causal=causal, per_block_mean=True, v_trick=True, check_status=True)
+    emu2 = sage3.sageattn4_emulated(q.cpu(), k.cpu(), v.cpu(), is_causal=causal, per_block_mean=True, v_trick=True)
+    cos, l1 = sage3.accuracy(out2.float().cpu(), emu2.float())
+    assert cos >= COS_MIN and l1 <= REL_L1_MAX, (cos, l1)
 
 
 @pytest.mark.parametrize("tag", ["s128", "s256"])
