@@ -77,6 +77,7 @@ typedef struct {
   size_t qm;        /* bf16 [B,Hq,Tq,D]  (per-block mean)  or [B,Hq,1,D] (whole-sequence mean)     */
   size_t km;        /* bf16 [B,Hkv,D]                                                              */
   size_t delta_s;   /* bf16 [B,Hq,Tq or 1,Tk*128]                                                  */
+  size_t q_dot_km;  /* fp32 [B,Hq,Nq]: raw q . K channel mean (the LSE term K smoothing removes)  */
   size_t scratch;   /* reduction scratch of the channel-mean kernel                               */
   size_t status;    /* one int32 on the device                                                    */
   size_t workspace; /* all of the above packed (256-byte aligned parts), for sage3_attention      */
@@ -96,6 +97,11 @@ typedef struct {
   void* delta_s;             /* out, optional: bf16(qm . k_smoothed^T), bf16 [B,Hq,Tq or 1,Tk*128]   */
   void* scratch;             /* >= sage3_sizes.scratch bytes, 256-byte aligned                       */
   size_t scratch_bytes;
+  int32_t* device_status;    /* optional device int32: a bounded wait of the delta_s kernel that gives up
+                                records a code in it (NOT zeroed by this call; read it back with
+                                sage3_read_device_status)                                            */
+  float* q_dot_km;           /* out, optional fp32 [B,Hq,Nq]: raw q . km of the row's kv head (needs smooth_k;
+                                dense batches) - feed it to sage3_attn_args.lse_add                   */
 } sage3_quant_args;
 
 typedef struct {
@@ -106,10 +112,13 @@ typedef struct {
   void* out;                 /* bf16, strides below (elements), last dim contiguous                  */
   int64_t out_stride_b, out_stride_h, out_stride_n;
   float* lse;                /* optional fp32 [B,Hq,Nq]: log-sum-exp (natural log) of the scores the
-                                kernel saw (after smoothing)                                         */
-  float sm_scale;
+                                kernel saw (after smoothing); -inf for rows that see no key          */
+  float sm_scale;            /* > 0                                                                  */
   int32_t is_causal;         /* bottom-right aligned when Nq != Nk (fwd_mainloop.cu:926)             */
   int32_t* device_status;    /* one int32 on the device; zeroed on the stream before the launch      */
+  const float* lse_add;      /* optional fp32 [B,Hq,Nq]: sm_scale * lse_add is added to the LSE - with
+                                sage3_quant_args.q_dot_km this undoes the shift K smoothing gives every
+                                score of a row (the pattern of sageattention/core.py:993-994)         */
 } sage3_attn_args;
 
 typedef struct {
@@ -117,8 +126,9 @@ typedef struct {
   sage3_tensor q, k, v;
   void* out;
   int64_t out_stride_b, out_stride_h, out_stride_n;
-  float* lse;                /* optional, see sage3_attn_args                                        */
-  void* km_out;              /* optional bf16 [B,Hkv,D]: K channel means (for an LSE correction)     */
+  float* lse;                /* optional fp32 [B,Hq,Nq]: log-sum-exp of sm_scale * q.k over the row (the K-mean
+                                term that smoothing removes is added back on the device)             */
+  void* km_out;              /* optional bf16 [B,Hkv,D]: K channel means (zeros when smooth_k == 0)   */
   float sm_scale;            /* <= 0: head_dim^-0.5                                                  */
   int32_t is_causal;
   int32_t per_block_mean;    /* as in sage3_quant_args                                               */

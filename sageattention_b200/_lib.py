@@ -28,7 +28,7 @@ class Tensor(C.Structure):
 class Sizes(C.Structure):
     _fields_ = [(n, C.c_size_t) for n in
                 ("q_codes", "q_sf", "k_codes", "k_sf", "vt_codes", "vt_sf", "qm", "km",
-                 "delta_s", "scratch", "status", "workspace")]
+                 "delta_s", "q_dot_km", "scratch", "status", "workspace")]
 
 
 class QuantArgs(C.Structure):
@@ -38,7 +38,8 @@ class QuantArgs(C.Structure):
                 ("q_codes", C.c_void_p), ("q_sf", C.c_void_p), ("k_codes", C.c_void_p), ("k_sf", C.c_void_p),
                 ("vt_codes", C.c_void_p), ("vt_sf", C.c_void_p),
                 ("qm", C.c_void_p), ("km", C.c_void_p), ("delta_s", C.c_void_p),
-                ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t)]
+                ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t), ("device_status", C.c_void_p),
+                ("q_dot_km", C.c_void_p)]
 
 
 class AttnArgs(C.Structure):
@@ -49,7 +50,7 @@ class AttnArgs(C.Structure):
                 ("out", C.c_void_p), ("out_stride_b", C.c_int64), ("out_stride_h", C.c_int64),
                 ("out_stride_n", C.c_int64),
                 ("lse", C.c_void_p), ("sm_scale", C.c_float), ("is_causal", C.c_int32),
-                ("device_status", C.c_void_p)]
+                ("device_status", C.c_void_p), ("lse_add", C.c_void_p)]
 
 
 class FwdArgs(C.Structure):

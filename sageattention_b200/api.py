@@ -288,14 +288,13 @@ def sageattn3_blackwell(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tenso
     _, _, _, _, osb, osh, osn = _as_bhnd_strides(out, tensor_layout)
     ws = torch.empty(int(z.workspace), dtype=torch.uint8, device=dev)
     lse = torch.empty((B, Hq, Nq), dtype=torch.float32, device=dev) if return_lse else None
-    km = torch.empty((B, Hkv, D), dtype=torch.bfloat16, device=dev) if (return_lse and smooth_k) else None
     status = torch.empty(1, dtype=torch.int32, device=dev)
     a = _lib.FwdArgs()
     a.shape = _lib.Shape(B, Hq, Hkv, Nq, Nk, D)
     a.q, a.k, a.v = _tensor_arg(q, qsb, qsh, qsn), _tensor_arg(k, ksb, ksh, ksn), _tensor_arg(v, vsb, vsh, vsn)
     a.out, a.out_stride_b, a.out_stride_h, a.out_stride_n = out.data_ptr(), osb, osh, osn
     a.lse = lse.data_ptr() if lse is not None else None
-    a.km_out = km.data_ptr() if km is not None else None
+    a.km_out = None           # the K-mean term of the LSE is put back on the device (q . km in the quantisation kernel)
     a.sm_scale = float(sm_scale) if sm_scale is not None else 0.0
     a.is_causal, a.per_block_mean, a.smooth_k = int(bool(is_causal)), pbm, int(bool(smooth_k))
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
@@ -304,15 +303,7 @@ def sageattn3_blackwell(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tenso
         _lib.check(lib.sage3_attention(C.byref(a), _stream_ptr(dev)), "sage3_attention")
         if check_status:
             _lib.check(lib.sage3_read_device_status(status.data_ptr(), _stream_ptr(dev), None), "attention kernel")
-    if not return_lse:
-        return out
-    if km is not None:
-        # the kernel saw scores q.(k - km); put the removed term back (core.py:993-994 pattern)
-        scale = float(sm_scale) if sm_scale is not None else D ** -0.5
-        qf = q.float() if tensor_layout == "HND" else q.float().transpose(1, 2)
-        kmf = km.float().repeat_interleave(Hq // Hkv, dim=1)
-        lse = lse + scale * torch.einsum("bhnd,bhd->bhn", qf, kmf)
-    return out, lse
+    return (out, lse) if return_lse else out
 
 
 def sageattn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND", is_causal: bool = False,

@@ -152,6 +152,7 @@ struct KParams {
   const __nv_bfloat16* ds;
   __nv_bfloat16* out;
   float* lse;
+  const float* lse_add;  // optional [B,Hq,Nq]: sm_scale * lse_add is added to the LSE (K-mean term removed by smoothing)
   int* status;
   int64_t o_sb, o_sh, o_sn;
   int B, Hq, Hkv, Nq, Nk, Tq, Tk, ds_rows;
@@ -874,8 +875,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         if (qpos < SEQ_NQ) {
           if (P.lse) {
             // natural-log sum of exp(sm_scale * s) over the row (l carries the factor 2688 / 2^kLazyLog2)
-            P.lse[((int64_t)wk.b * P.Hq + wk.hq) * P.Nq + qpos] =
-                (l == 0.f) ? -INFINITY : (m_ref * c + log2f(l) + kLog2InvTop) * (1.0f / kLog2e);
+            const int64_t li = ((int64_t)wk.b * P.Hq + wk.hq) * P.Nq + qpos;
+            float v = (l == 0.f) ? -INFINITY : (m_ref * c + log2f(l) + kLog2InvTop) * (1.0f / kLog2e);
+            if (P.lse_add != nullptr) v = fmaf(P.lse_add[li], c * (1.0f / kLog2e), v);
+            P.lse[li] = v;
           }
         }
       }
@@ -968,7 +971,7 @@ cudaError_t launch(const AttnArgs& a, cudaStream_t stream) {
     return cudaErrorInvalidValue;
   KParams P;
   P.q_sf = (const uint8_t*)a.q_sf; P.k_sf = (const uint8_t*)a.k_sf; P.vt_sf = (const uint8_t*)a.vt_sf;
-  P.ds = (const __nv_bfloat16*)a.ds; P.out = (__nv_bfloat16*)a.out; P.lse = a.lse; P.status = a.status;
+  P.ds = (const __nv_bfloat16*)a.ds; P.out = (__nv_bfloat16*)a.out; P.lse = a.lse; P.lse_add = a.lse_add; P.status = a.status;
   P.o_sb = a.o_sb; P.o_sh = a.o_sh; P.o_sn = a.o_sn;
   P.B = a.B; P.Hq = a.Hq; P.Hkv = a.Hkv; P.Nq = a.Nq; P.Nk = a.Nk; P.Tq = Tq; P.Tk = Tk; P.ds_rows = a.ds_rows;
   P.scale_log2 = a.sm_scale * kLog2e;

@@ -76,13 +76,14 @@ int sage3_buffer_sizes(const sage3_shape* shape, int per_block_mean, sage3_sizes
   out->qm = bhq * ds_rows * s.D * 2;
   out->km = bhk * s.D * 2;
   out->delta_s = per_block_mean < 0 ? 0 : bhq * ds_rows * Tk * 128 * 2;
+  out->q_dot_km = bhq * (size_t)s.Nq * sizeof(float);
   size_t sk = sage3::quant_scratch_bytes(s.B, s.Hkv, s.Nk, s.D);
   size_t sq = sage3::quant_scratch_bytes(s.B, s.Hq, s.Nq, s.D);
   out->scratch = sk > sq ? sk : sq;
   out->status = 4;
   out->workspace = align256(out->q_codes) + align256(out->q_sf) + align256(out->k_codes) + align256(out->k_sf) +
                    align256(out->vt_codes) + align256(out->vt_sf) + align256(out->qm) + align256(out->km) +
-                   align256(out->delta_s) + align256(out->scratch) + 256;
+                   align256(out->delta_s) + align256(out->q_dot_km) + align256(out->scratch) + 256;
   return SAGE3_OK;
 }
 
@@ -125,8 +126,11 @@ static int quant_qkv_impl(const sage3_quant_args* a, const int* cu_q, const int*
     if (e != cudaSuccess) return cuda_fail(e);
   }
 
+  // with delta_s requested, K is quantised by the delta_s kernel, which has the smoothed tile in hand anyway
+  const bool k_in_ds = a->delta_s != nullptr && a->k.ptr != nullptr;
+  if (a->delta_s != nullptr && (!a->q.ptr || !a->k.ptr || a->per_block_mean < 0)) return SAGE3_ERR_ARGUMENT;
   sage3::QuantArgs q{};
-  q.q = a->q.ptr; q.k = a->k.ptr; q.v = a->v.ptr;
+  q.q = a->q.ptr; q.k = k_in_ds ? nullptr : a->k.ptr; q.v = a->v.ptr;
   q.q_sb = a->q.stride_b; q.q_sh = a->q.stride_h; q.q_sn = a->q.stride_n;
   q.k_sb = a->k.stride_b; q.k_sh = a->k.stride_h; q.k_sn = a->k.stride_n;
   q.v_sb = a->v.stride_b; q.v_sh = a->v.stride_h; q.v_sn = a->v.stride_n;
@@ -138,14 +142,18 @@ static int quant_qkv_impl(const sage3_quant_args* a, const int* cu_q, const int*
   q.q_codes = a->q_codes; q.q_sf = a->q_sf; q.k_codes = a->k_codes; q.k_sf = a->k_sf;
   q.vt_codes = a->vt_codes; q.vt_sf = a->vt_sf; q.qm = a->qm;
   q.cu_q = cu_q; q.cu_k = cu_k;
+  if (a->q_dot_km != nullptr) {
+    if (km == nullptr || cu_q != nullptr || !a->q.ptr) return SAGE3_ERR_ARGUMENT;
+    q.q_dot_km = a->q_dot_km;
+  }
   cudaError_t e = sage3::launch_quant_qkv(q, stream);
   if (e != cudaSuccess) return cuda_fail(e);
 
   if (a->delta_s != nullptr) {
-    if (!a->q.ptr || !a->k.ptr || a->per_block_mean < 0) return SAGE3_ERR_ARGUMENT;
     sage3::DeltaSArgs d{};
     d.qm = a->qm; d.k = a->k.ptr; d.k_sb = a->k.stride_b; d.k_sh = a->k.stride_h; d.k_sn = a->k.stride_n;
     d.km = km; d.ds = a->delta_s; d.cu_k = cu_k;
+    d.k_codes = a->k_codes; d.k_sf = a->k_sf; d.status = a->device_status;
     d.B = s.B; d.Hq = s.Hq; d.Hkv = s.Hkv; d.Tq = a->per_block_mean == 1 ? Tq : 1; d.Nk = s.Nk; d.D = s.D;
     e = sage3::launch_delta_s(d, stream);
     if (e != cudaSuccess) return cuda_fail(e);
@@ -156,7 +164,7 @@ static int quant_qkv_impl(const sage3_quant_args* a, const int* cu_q, const int*
 int sage3_quant_qkv(const sage3_quant_args* a, void* stream) { return quant_qkv_impl(a, nullptr, nullptr, stream); }
 
 static int attn_fwd_impl(const sage3_attn_args* a, const float* k_lambda, const int* cu_q, const int* cu_k, void* stream_,
-                         int slot_first = 0) {
+                         int slot_first = 0, bool zero_status = true) {
   if (a == nullptr) return SAGE3_ERR_ARGUMENT;
   if (int st = check_shape(a->shape)) return st;
   if (!a->q_codes || !a->q_sf || !a->k_codes || !a->k_sf || !a->vt_codes || !a->vt_sf || !a->out || !a->device_status)
@@ -170,13 +178,16 @@ static int attn_fwd_impl(const sage3_attn_args* a, const float* k_lambda, const 
   if (a->delta_s && a->delta_s_rows != 1 && a->delta_s_rows != Tq) return SAGE3_ERR_ARGUMENT;
   if (!(a->sm_scale > 0.f)) return SAGE3_ERR_ARGUMENT;          // the row maximum is tracked in raw score units
   cudaStream_t stream = (cudaStream_t)stream_;
-  cudaError_t e = cudaMemsetAsync(a->device_status, 0, sizeof(int32_t), stream);
-  if (e != cudaSuccess) return cuda_fail(e);
+  cudaError_t e = cudaSuccess;
+  if (zero_status) {
+    e = cudaMemsetAsync(a->device_status, 0, sizeof(int32_t), stream);
+    if (e != cudaSuccess) return cuda_fail(e);
+  }
   sage3::AttnArgs k{};
   k.q_codes = a->q_codes; k.q_sf = a->q_sf; k.k_codes = a->k_codes; k.k_sf = a->k_sf;
   k.vt_codes = a->vt_codes; k.vt_sf = a->vt_sf; k.ds = a->delta_s; k.ds_rows = a->delta_s ? a->delta_s_rows : 1;
   k.out = a->out; k.o_sb = a->out_stride_b; k.o_sh = a->out_stride_h; k.o_sn = a->out_stride_n;
-  k.lse = a->lse; k.status = a->device_status;
+  k.lse = a->lse; k.lse_add = a->lse_add; k.status = a->device_status;
   k.B = s.B; k.Hq = s.Hq; k.Hkv = s.Hkv; k.Nq = s.Nq; k.Nk = s.Nk; k.D = s.D;
   k.sm_scale = a->sm_scale; k.causal = a->is_causal;
   k.k_lambda = k_lambda;
@@ -250,11 +261,19 @@ int sage3_attention(const sage3_fwd_args* a, void* stream) {
   void* km_ws = take(z.km);
   q.km = a->km_out ? a->km_out : km_ws;
   void* ds = take(z.delta_s);
+  float* qk = reinterpret_cast<float*>(take(z.q_dot_km));
   q.scratch = take(z.scratch); q.scratch_bytes = z.scratch;
   int32_t* status = reinterpret_cast<int32_t*>(take(4));
   if (a->device_status) status = a->device_status;
+  if (a->lse && a->smooth_k) q.q_dot_km = qk;
   const float sm_scale = a->sm_scale > 0.f ? a->sm_scale : 1.0f / sqrtf((float)a->shape.D);
   q.delta_s = a->per_block_mean >= 0 ? ds : nullptr;
+  // one status word for the whole call: zeroed here, the preprocessing kernels and the attention kernel report in it
+  q.device_status = status;
+  {
+    cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int32_t), (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e);
+  }
   if (a->km_out && !a->smooth_k) {
     // no mean is removed: the caller's LSE correction term must vanish
     cudaError_t e = cudaMemsetAsync(a->km_out, 0, z.km, (cudaStream_t)stream);
@@ -268,7 +287,8 @@ int sage3_attention(const sage3_fwd_args* a, void* stream) {
   t.delta_s_rows = a->per_block_mean == 1 ? (a->shape.Nq + 127) / 128 : 1;
   t.out = a->out; t.out_stride_b = a->out_stride_b; t.out_stride_h = a->out_stride_h; t.out_stride_n = a->out_stride_n;
   t.lse = a->lse; t.sm_scale = sm_scale; t.is_causal = a->is_causal; t.device_status = status;
-  return sage3_attn_fwd(&t, stream);
+  t.lse_add = q.q_dot_km;
+  return attn_fwd_impl(&t, nullptr, nullptr, nullptr, stream, 0, /*zero_status=*/false);
 }
 
 int sage3_attention_varlen(const sage3_varlen_args* a, void* stream) {
@@ -291,9 +311,15 @@ int sage3_attention_varlen(const sage3_varlen_args* a, void* stream) {
   q.qm = take(z.qm);
   q.km = take(z.km);
   q.delta_s = take(z.delta_s);
+  take(z.q_dot_km);                                   // no LSE for packed batches (the reference returns none)
   q.scratch = take(z.scratch); q.scratch_bytes = z.scratch;
   int32_t* status = reinterpret_cast<int32_t*>(take(4));
   if (a->device_status) status = a->device_status;
+  q.device_status = status;
+  {
+    cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int32_t), (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e);
+  }
   if (int st = quant_qkv_impl(&q, a->cu_seqlens_q, a->cu_seqlens_k, stream)) return st;
   sage3_attn_args t{};
   t.shape = a->shape;
@@ -304,7 +330,7 @@ int sage3_attention_varlen(const sage3_varlen_args* a, void* stream) {
   t.lse = nullptr;
   t.sm_scale = a->sm_scale > 0.f ? a->sm_scale : 1.0f / sqrtf((float)a->shape.D);
   t.is_causal = a->is_causal; t.device_status = status;
-  return attn_fwd_impl(&t, nullptr, a->cu_seqlens_q, a->cu_seqlens_k, stream);
+  return attn_fwd_impl(&t, nullptr, a->cu_seqlens_q, a->cu_seqlens_k, stream, 0, /*zero_status=*/false);
 }
 
 int sage3_k_mean_static(const sage3_shape* shape, const sage3_tensor* k, void* km_out, void* stream) {

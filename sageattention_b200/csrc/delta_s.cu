@@ -1,143 +1,200 @@
-// delta_s[b, hq, qb, n] = bf16( sum_d qm[b, hq, qb, d] * ks[b, hkv, n, d] ),  ks = bf16(k - km)
+// K quantisation + delta_s in one pass over K:
+//   ks            = bf16(k - km)                                       sageattn4/api.py:184
+//   K codes / SF  = NVFP4(ks), 128-token tiles                         quantization/fp4_quantization_4d.cu:492-569
+//   delta_s[b, hq, qb, n] = bf16( sum_d qm[b, hq, qb, d] * ks[b, hkv, n, d] )   api.py:201
 //
-// Replaces `delta_s = torch.matmul(qm, k.transpose(-2, -1)).to(torch.float32)` of
-// sageattn4/api.py:201: a bf16 GEMM (fp32 accumulation, bf16 result) that the reference then
-// widens to fp32.  It stays bf16 here - the same values in half the bytes - because the
-// attention kernel feeds each row to the tensor core as a bf16 operand (rank-1 update of the
-// score accumulator), which restores the Q block mean that was removed before quantisation.
+// The reference computes delta_s with a bf16 GEMM (fp32 accumulation, bf16 result) that it then widens to fp32.
+// It stays bf16 here - the same values in half the bytes - because the attention kernel feeds each row to the
+// tensor core as a bf16 operand (rank-1 update of the score accumulator), which restores the Q block mean that
+// was removed before quantisation.
 //
-// One CTA per (128-key tile, kv head): the smoothed K tile is rebuilt in shared memory once and
-// multiplied against the block means of every query head of the GQA group.  The output
-// ([Tq x 128] bf16 per CTA and head) dominates the traffic, so the small contraction runs on
-// mma.sync m16n8k16 with fragments read straight from shared memory, and results are staged per
-// warp so that they leave as whole 256-byte rows.
+// One CTA per (128-key tile, kv head): the K tile is read from HBM ONCE, smoothed in registers, quantised (the
+// same device function as the fused quantisation kernel, so codes and scales are bit-identical) and laid out
+// in shared memory as the B operand of tcgen05.mma kind::f16; the Q block means of every query head of the GQA
+// group (rows of A, 128 query blocks at a time) are multiplied against it with the accumulator in tensor
+// memory, and every thread writes 128 contiguous bytes of a delta_s row.  HBM-bound: the output
+// ([Tq x 128] bf16 per CTA and query head) dominates the traffic.
+//
+// Operand layout in shared memory (K-major, no swizzle): 8-row x 16-byte core matrices; the 16 row groups of one
+// 8-channel chunk are contiguous (128 B apart), chunks are kChunk bytes apart - 16 bytes more than their size so
+// that the 16 lanes which write one row's chunks hit different banks.
 #include "common.cuh"
 #include "kernels.h"
+#include "quant_rows.cuh"
 
 namespace sage3 {
 
+namespace {
+
+constexpr uint32_t kChunk = 128 * 16 + 16;            // one 8-channel chunk of 128 rows (+ bank skew)
+
+struct KDsParams {
+  const __nv_bfloat16 *qm, *k, *km;
+  int64_t k_sb, k_sh, k_sn;
+  uint8_t *k_codes, *k_sf;                             // null: K is quantised elsewhere
+  __nv_bfloat16* ds;
+  int* status;                                         // optional device status word
+  int Hq, Hkv, Tq, Tk, Nk;
+  const int* cu_k;
+};
+
 template <int D>
-__global__ void __launch_bounds__(256, 3) delta_s_kernel(
-    const __nv_bfloat16* __restrict__ qm, const __nv_bfloat16* __restrict__ k, int64_t k_sb, int64_t k_sh,
-    int64_t k_sn, const __nv_bfloat16* __restrict__ km, __nv_bfloat16* __restrict__ ds, int Hq, int Hkv, int Tq,
-    int Nk, int Nk_pad, const int* __restrict__ cu_k) {
-  constexpr int PITCH = D + 8;                         // bf16 elements; 4-bank skew per row
-  extern __shared__ __align__(16) unsigned char dyn_smem[];
-  __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(dyn_smem);              // [128][PITCH]
-  __nv_bfloat16* cs = ks + 128 * PITCH;                                        // [8 warps][16][136]
-  const int tile = blockIdx.x, bh = blockIdx.y, b = bh / Hkv, hkv = bh % Hkv, G = Hq / Hkv;
-  const int t = threadIdx.x, warp = t >> 5, lane = t & 31, g = lane >> 2, tg = lane & 3;
+__global__ void __launch_bounds__(kThreads, 2) k_quant_delta_s_kernel(const KDsParams P) {
+  constexpr int CH = D / 8, RPP = kThreads / CH, NP = kTile / RPP;
+  constexpr uint32_t kTileBytes = CH * kChunk;
+  extern __shared__ __align__(16) uint8_t dyn_smem[];
+  uint8_t* sB = dyn_smem;                              // smoothed K tile  [CH][kChunk]
+  uint8_t* sA = dyn_smem + kTileBytes;                 // 128 Q block means [CH][kChunk]
+  uint8_t* sf_smem = sA + kTileBytes;                  // 2048 B
+  uint8_t* misc = sf_smem + 2048;                      // mbarrier (8 B), tensor-memory slot (4 B), abort flag (4 B)
+  const uint32_t bar = smem_u32(misc), slot = smem_u32(misc + 8);
+  int* abort_s = reinterpret_cast<int*>(misc + 12);
+  const int tile = blockIdx.x, bh = blockIdx.y, b = bh / P.Hkv, hkv = bh % P.Hkv, G = P.Hq / P.Hkv;
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31, c = t % CH, rl = t / CH;
 
-  // A fragments (rows m0+g and m0+g+8 of the stacked block means of this GQA group) come from global memory /
-  // L2; the first set is requested before the K tile is built and the next one while the current one is
-  // multiplied, so their latency is not on the critical path
-  const int M = G * Tq;
-  auto load_a = [&](uint32_t (&a)[D / 16][4], const int m0) {
-    const int r0 = m0 + g, r1 = m0 + g + 8;
-    const uint32_t* p0 = nullptr; const uint32_t* p1 = nullptr;
-    if (r0 < M) p0 = reinterpret_cast<const uint32_t*>(qm + (((int64_t)b * Hq + hkv * G + r0 / Tq) * Tq + r0 % Tq) * D);
-    if (r1 < M) p1 = reinterpret_cast<const uint32_t*>(qm + (((int64_t)b * Hq + hkv * G + r1 / Tq) * Tq + r1 % Tq) * D);
-#pragma unroll
-    for (int s = 0; s < D / 16; ++s) {
-      a[s][0] = p0 ? __ldg(p0 + s * 8 + tg) : 0u;
-      a[s][1] = p1 ? __ldg(p1 + s * 8 + tg) : 0u;
-      a[s][2] = p0 ? __ldg(p0 + s * 8 + 4 + tg) : 0u;
-      a[s][3] = p1 ? __ldg(p1 + s * 8 + 4 + tg) : 0u;
-    }
-  };
-  uint32_t a_next[D / 16][4];
-  load_a(a_next, warp * 16);
+  if (t == 0) {
+    mbar_init(bar, 1);
+    *abort_s = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(slot, 128);
+    tmem_relinquish();
+  }
 
-  {  // smoothed K tile -> shared
-    constexpr int CH = D / 8, RPP = 256 / CH;
-    const int c = t % CH, rl = t / CH;
-    float mean[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (km != nullptr) {
-      uint4 m = *reinterpret_cast<const uint4*>(km + (int64_t)bh * D + c * 8);
-      mean[0] = bf16_lo(m.x); mean[1] = bf16_hi(m.x); mean[2] = bf16_lo(m.y); mean[3] = bf16_hi(m.y);
-      mean[4] = bf16_lo(m.z); mean[5] = bf16_hi(m.z); mean[6] = bf16_lo(m.w); mean[7] = bf16_hi(m.w);
-    }
-    // variable-length batch: sequence b starts at token cu_k[b] of the packed tensor and has its own length
-    if (cu_k != nullptr) Nk = min(cu_k[b + 1] - cu_k[b], Nk);   // cut at max_seqlen like every other kernel
-    const __nv_bfloat16* src = k + (cu_k ? (int64_t)cu_k[b] * k_sn : b * k_sb) + hkv * k_sh + c * 8;
-    uint4 w[128 / RPP];
+  // ---- the K tile: load, smooth, quantise, lay out as the B operand
+  int Nk = P.Nk;
+  if (P.cu_k != nullptr) Nk = min(P.cu_k[b + 1] - P.cu_k[b], Nk);   // a packed batch: this sequence, cut at max_seqlen
+  const __nv_bfloat16* src = P.k + (P.cu_k ? (int64_t)P.cu_k[b] * P.k_sn : b * P.k_sb) + hkv * P.k_sh + c * 8;
+  uint4 w[NP];
 #pragma unroll
-    for (int p = 0; p < 128 / RPP; ++p) {                  // all loads in flight before the first use
-      const int n = tile * 128 + p * RPP + rl;
-      w[p] = make_uint4(0, 0, 0, 0);
-      if (n < Nk) w[p] = *reinterpret_cast<const uint4*>(src + (int64_t)n * k_sn);
-    }
+  for (int p = 0; p < NP; ++p) {                       // all loads in flight before the first use
+    const int n = tile * kTile + p * RPP + rl;
+    w[p] = n < Nk ? *reinterpret_cast<const uint4*>(src + (int64_t)n * P.k_sn) : make_uint4(0, 0, 0, 0);
+  }
+  if (P.km != nullptr) {
+    const uint4 m = *reinterpret_cast<const uint4*>(P.km + (int64_t)bh * D + c * 8);
+    const float mean[8] = {bf16_lo(m.x), bf16_hi(m.x), bf16_lo(m.y), bf16_hi(m.y),
+                           bf16_lo(m.z), bf16_hi(m.z), bf16_lo(m.w), bf16_hi(m.w)};
 #pragma unroll
-    for (int p = 0; p < 128 / RPP; ++p) {
-      const int r = p * RPP + rl, n = tile * 128 + r;
-      uint4 x = w[p];
-      if (n < Nk) {
-        x.x = pack_bf16(bf16_lo(x.x) - mean[0], bf16_hi(x.x) - mean[1]);
-        x.y = pack_bf16(bf16_lo(x.y) - mean[2], bf16_hi(x.y) - mean[3]);
-        x.z = pack_bf16(bf16_lo(x.z) - mean[4], bf16_hi(x.z) - mean[5]);
-        x.w = pack_bf16(bf16_lo(x.w) - mean[6], bf16_hi(x.w) - mean[7]);
+    for (int p = 0; p < NP; ++p) {
+      if (tile * kTile + p * RPP + rl < Nk) {          // padding rows stay zero (the reference subtracts before padding)
+        w[p].x = pack_bf16(bf16_lo(w[p].x) - mean[0], bf16_hi(w[p].x) - mean[1]);
+        w[p].y = pack_bf16(bf16_lo(w[p].y) - mean[2], bf16_hi(w[p].y) - mean[3]);
+        w[p].z = pack_bf16(bf16_lo(w[p].z) - mean[4], bf16_hi(w[p].z) - mean[5]);
+        w[p].w = pack_bf16(bf16_lo(w[p].w) - mean[6], bf16_hi(w[p].w) - mean[7]);
       }
-      *reinterpret_cast<uint4*>(&ks[r * PITCH + c * 8]) = x;
     }
   }
+#pragma unroll
+  for (int p = 0; p < NP; ++p) {
+    const int row = p * RPP + rl;
+    *reinterpret_cast<uint4*>(sB + c * kChunk + (row >> 3) * 128 + (row & 7) * 16) = w[p];
+  }
+  if (P.k_codes != nullptr) {
+    const int64_t kt = (int64_t)bh * P.Tk + tile;
+    quant_rows_store<D>(w, P.k_codes + kt * (kTile * D / 2), P.k_sf + kt * ((D / 64) * 512), sf_smem);
+  }
+  tc_fence_before();
   __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(misc + 8);
 
-  const uint32_t* ks32 = reinterpret_cast<const uint32_t*>(ks);
-  for (int m0 = warp * 16; m0 < M; m0 += 8 * 16) {
-    uint32_t a[D / 16][4];
+  // ---- delta_s: for every query head of the group, 128 query blocks at a time
+  constexpr uint32_t idesc = make_idesc_bf16(128, 128);
+  constexpr uint32_t HI = (128u >> 4) | (1u << 14);                     // 8-row groups 128 B apart, no swizzle
+  const uint32_t a_lo = (smem_u32(sA) >> 4) | ((kChunk >> 4) << 16);    // leading (K) offset = one chunk
+  const uint32_t b_lo = (smem_u32(sB) >> 4) | ((kChunk >> 4) << 16);
+  const int n_mb = (P.Tq + 127) / 128;
+  const int Nk_pad = P.Tk * kTile;
+  uint32_t iter = 0;
+  bool ok = true;
+  for (int hg = 0; hg < G && ok; ++hg) {
+    const int hq = hkv * G + hg;
+    const __nv_bfloat16* qm_h = P.qm + ((int64_t)b * P.Hq + hq) * P.Tq * D;
+    __nv_bfloat16* ds_h = P.ds + ((int64_t)b * P.Hq + hq) * P.Tq * Nk_pad + tile * kTile;
+    for (int mb = 0; mb < n_mb && ok; ++mb, ++iter) {
+      // A: block means of query blocks mb*128 ... +127 (zeros beyond the last one)
 #pragma unroll
-    for (int s = 0; s < D / 16; ++s)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) a[s][i] = a_next[s][i];
-    if (m0 + 8 * 16 < M) load_a(a_next, m0 + 8 * 16);
-    __nv_bfloat16* cw = cs + warp * (16 * 136);
-#pragma unroll 4
-    for (int nt = 0; nt < 16; ++nt) {
-      float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
-      const uint32_t* brow = ks32 + (nt * 8 + g) * (PITCH / 2) + tg;
-#pragma unroll
-      for (int s = 0; s < D / 16; ++s) {
-        uint32_t b0 = brow[s * 8], b1 = brow[s * 8 + 4];
-        asm volatile(
-            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-            : "+f"(c0), "+f"(c1), "+f"(c2), "+f"(c3)
-            : "r"(a[s][0]), "r"(a[s][1]), "r"(a[s][2]), "r"(a[s][3]), "r"(b0), "r"(b1));
+      for (int p = 0; p < NP; ++p) {
+        const int row = p * RPP + rl, m = mb * 128 + row;
+        const uint4 v = m < P.Tq ? __ldg(reinterpret_cast<const uint4*>(qm_h + (int64_t)m * D + c * 8)) : make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(sA + c * kChunk + (row >> 3) * 128 + (row & 7) * 16) = v;
       }
-      *reinterpret_cast<uint32_t*>(&cw[g * 136 + nt * 8 + tg * 2]) = pack_bf16(c0, c1);
-      *reinterpret_cast<uint32_t*>(&cw[(g + 8) * 136 + nt * 8 + tg * 2]) = pack_bf16(c2, c3);
-    }
-    __syncwarp();
-    // 16 rows x 256 bytes leave as whole rows: two rows per warp store instruction
+      fence_proxy_async_smem();
+      __syncthreads();
+      if (t == 0) {
+        tc_fence_after();
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int r = i * 2 + (lane >> 4), m = m0 + r;
-      if (m < M) {
-        uint4 v = *reinterpret_cast<const uint4*>(&cw[r * 136 + (lane & 15) * 8]);
-        __nv_bfloat16* dst = ds + ((((int64_t)b * Hq + hkv * G + m / Tq) * Tq + m % Tq) * Nk_pad + tile * 128);
-        reinterpret_cast<uint4*>(dst)[lane & 15] = v;
+        for (int kk = 0; kk < D / 16; ++kk)            // K = 16 per instruction = two chunks
+          tc_mma_bf16(tmem, a_lo + kk * (2 * kChunk >> 4), HI, b_lo + kk * (2 * kChunk >> 4), HI, idesc, kk > 0 ? 1u : 0u);
+        tc_commit(bar);
       }
+      // bounded: a few microseconds normally; gives up after about a second
+      if (P.status != nullptr) {
+        ok = wait_bar<false, (1u << 19)>(bar, iter & 1, abort_s, P.status, 50);
+      } else {
+        ok = mbar_wait(bar, iter & 1, 1u << 19);
+      }
+      ok = __all_sync(0xffffffffu, ok);                // the tensor-memory loads below are warp-wide
+      tc_fence_after();
+      if (ok) {
+        // lane = query block, 64 columns (keys) per thread: warps 0-3 take keys 0-63, warps 4-7 keys 64-127
+        const int m = mb * 128 + (warp & 3) * 32 + lane;
+        const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(warp >> 2) * 64;
+        uint32_t r0[32], r1[32];
+        tmem_ld32(taddr, r0);
+        tmem_ld32(taddr + 32, r1);
+        tmem_wait_ld();
+        if (m < P.Tq) {
+          uint4* dst = reinterpret_cast<uint4*>(ds_h + (int64_t)m * Nk_pad + (warp >> 2) * 64);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            dst[i] = make_uint4(pack_bf16(__uint_as_float(r0[8 * i]), __uint_as_float(r0[8 * i + 1])),
+                                pack_bf16(__uint_as_float(r0[8 * i + 2]), __uint_as_float(r0[8 * i + 3])),
+                                pack_bf16(__uint_as_float(r0[8 * i + 4]), __uint_as_float(r0[8 * i + 5])),
+                                pack_bf16(__uint_as_float(r0[8 * i + 6]), __uint_as_float(r0[8 * i + 7])));
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            dst[4 + i] = make_uint4(pack_bf16(__uint_as_float(r1[8 * i]), __uint_as_float(r1[8 * i + 1])),
+                                    pack_bf16(__uint_as_float(r1[8 * i + 2]), __uint_as_float(r1[8 * i + 3])),
+                                    pack_bf16(__uint_as_float(r1[8 * i + 4]), __uint_as_float(r1[8 * i + 5])),
+                                    pack_bf16(__uint_as_float(r1[8 * i + 6]), __uint_as_float(r1[8 * i + 7])));
+        }
+      }
+      // the accumulator and the A tile are rewritten by the next round; every thread leaves the loop together
+      tc_fence_before();
+      ok = __syncthreads_and(ok);
     }
-    __syncwarp();
   }
+  if (!ok && t == 0) {
+    // the MMAs issued last may still be running: give them time to drain before tensor memory is freed
+    mbar_wait(bar, iter & 1, 1u << 16);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 128);
 }
 
+}  // namespace
+
 cudaError_t launch_delta_s(const DeltaSArgs& a, cudaStream_t stream) {
-  const int Tk = (a.Nk + 127) / 128;
-  dim3 grid(Tk, a.B * a.Hkv);
-  const int smem = (128 * (a.D + 8) + 8 * 16 * 136) * 2;
+  KDsParams P;
+  P.qm = (const __nv_bfloat16*)a.qm; P.k = (const __nv_bfloat16*)a.k; P.km = (const __nv_bfloat16*)a.km;
+  P.k_sb = a.k_sb; P.k_sh = a.k_sh; P.k_sn = a.k_sn;
+  P.k_codes = (uint8_t*)a.k_codes; P.k_sf = (uint8_t*)a.k_sf;
+  P.ds = (__nv_bfloat16*)a.ds; P.status = a.status;
+  P.Hq = a.Hq; P.Hkv = a.Hkv; P.Tq = a.Tq; P.Nk = a.Nk; P.Tk = (a.Nk + 127) / 128;
+  P.cu_k = a.cu_k;
+  dim3 grid(P.Tk, a.B * a.Hkv);
+  const int smem = 2 * (a.D / 8) * (int)kChunk + 2048 + 16;
   // per device and cheap, so set on every call rather than cached per process
   cudaError_t e = a.D == 128
-      ? cudaFuncSetAttribute(delta_s_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
-      : cudaFuncSetAttribute(delta_s_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      ? cudaFuncSetAttribute(k_quant_delta_s_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
+      : cudaFuncSetAttribute(k_quant_delta_s_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  if (a.D == 128)
-    delta_s_kernel<128><<<grid, 256, smem, stream>>>((const __nv_bfloat16*)a.qm, (const __nv_bfloat16*)a.k, a.k_sb, a.k_sh,
-                                                  a.k_sn, (const __nv_bfloat16*)a.km, (__nv_bfloat16*)a.ds, a.Hq, a.Hkv,
-                                                  a.Tq, a.Nk, Tk * 128, a.cu_k);
-  else
-    delta_s_kernel<64><<<grid, 256, smem, stream>>>((const __nv_bfloat16*)a.qm, (const __nv_bfloat16*)a.k, a.k_sb, a.k_sh,
-                                                 a.k_sn, (const __nv_bfloat16*)a.km, (__nv_bfloat16*)a.ds, a.Hq, a.Hkv,
-                                                 a.Tq, a.Nk, Tk * 128, a.cu_k);
+  if (a.D == 128) k_quant_delta_s_kernel<128><<<grid, kThreads, smem, stream>>>(P);
+  else            k_quant_delta_s_kernel<64><<<grid, kThreads, smem, stream>>>(P);
   return cudaGetLastError();
 }
 

@@ -15,6 +15,7 @@ struct QuantArgs {
   const void* q_mean_seq;                 // bf16 [B,Hq,D]   (mode 2)
   const void* qm_override;                // fp32 [B,Hq,Tq,D] or null (mode 1)
   void *q_codes, *q_sf, *k_codes, *k_sf, *vt_codes, *vt_sf, *qm;
+  void* q_dot_km = nullptr;               // optional fp32 [B,Hq,Nq]: raw q . km (needs km; dense batches only)
   // variable-length batches: device int32 [B+1] token offsets of the sequences inside packed [tokens, H, D]
   // tensors (then *_sb is ignored and Nq / Nk are the LONGEST sequence, which sizes the output layouts)
   const int* cu_q = nullptr;
@@ -49,6 +50,9 @@ struct DeltaSArgs {
   void* ds;                               // bf16 [B,Hq,Tq,Nk_pad]
   int B, Hq, Hkv, Tq, Nk, D;
   const int* cu_k = nullptr;              // variable-length batches, see QuantArgs
+  void* k_codes = nullptr;                // when given, the kernel also writes the NVFP4 codes and scales of the
+  void* k_sf = nullptr;                   //   smoothed K tile it holds (the K role of the quantisation kernel)
+  int* status = nullptr;                  // optional device status word for the kernel's bounded wait
 };
 cudaError_t launch_delta_s(const DeltaSArgs& a, cudaStream_t stream);
 
@@ -59,6 +63,7 @@ struct AttnArgs {
   void* out;                              // bf16, strides below
   int64_t o_sb, o_sh, o_sn;
   float* lse;                             // fp32 [B,Hq,Nq] or null
+  const float* lse_add = nullptr;         // optional fp32 [B,Hq,Nq]: sm_scale times it is added to the LSE
   int* status;                            // device int, set non-zero if a bounded wait gave up
   int B, Hq, Hkv, Nq, Nk, D;
   float sm_scale;

@@ -25,11 +25,9 @@
 //   qm         : [T][D] bf16 block means of Q;  km : [D] bf16 channel means of K
 #include "common.cuh"
 #include "kernels.h"
+#include "quant_rows.cuh"
 
 namespace sage3 {
-
-constexpr int kTile = 128;
-constexpr int kThreads = 256;
 
 // ------------------------------------------------------------------------------------------------
 // Channel sums over tokens (K channel mean; also the whole-sequence Q mean when per_block_mean=0).
@@ -99,39 +97,6 @@ __global__ void __launch_bounds__(kThreads) channel_mean_kernel(
   }
 }
 
-// ------------------------------------------------------------------------------------------------
-// Row-wise quantisation of one 128-token tile held in registers (Q and K roles).
-// Thread t owns 8 consecutive channels (chunk c) of rows rl, rl+RPP, ... ; w[p] = 4 packed bf16x2.
-// ------------------------------------------------------------------------------------------------
-template <int D>
-__device__ __forceinline__ void quant_rows_store(const uint4 (&w)[kTile / (kThreads / (D / 8))],
-                                                 uint8_t* __restrict__ codes_tile, uint8_t* __restrict__ sf_tile,
-                                                 uint8_t* sf_smem) {
-  constexpr int CH = D / 8, RPP = kThreads / CH, NP = kTile / RPP;
-  const int t = threadIdx.x, c = t % CH, rl = t / CH;
-#pragma unroll
-  for (int p = 0; p < NP; ++p) {
-    const int row = p * RPP + rl;
-    uint32_t m2 = habsmax2(habsmax2(w[p].x, w[p].y), habsmax2(w[p].z, w[p].w));
-    float amax = fmaxf(bf16_lo(m2), bf16_hi(m2));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));       // 16-element block = 2 threads
-    uint32_t sfb; float inv;
-    block_scale(amax, sfb, inv);
-    uint32_t code = f32x8_to_e2m1x8(
-        mul_ftz(bf16_lo(w[p].x), inv), mul_ftz(bf16_hi(w[p].x), inv), mul_ftz(bf16_lo(w[p].y), inv),
-        mul_ftz(bf16_hi(w[p].y), inv), mul_ftz(bf16_lo(w[p].z), inv), mul_ftz(bf16_hi(w[p].z), inv),
-        mul_ftz(bf16_lo(w[p].w), inv), mul_ftz(bf16_hi(w[p].w), inv));
-    *reinterpret_cast<uint32_t*>(codes_tile + row * (D / 2) + c * 4) = code;
-    if ((c & 1) == 0) {
-      const int blk = c >> 1;                                        // 16-channel block index
-      sf_smem[(blk >> 2) * 512 + sf_atom_offset(row, blk & 3)] = (uint8_t)sfb;
-    }
-  }
-  __syncthreads();
-  constexpr int SFV = (D / 64) * 512 / 16;                           // 16-byte vectors of scales
-  if (t < SFV) reinterpret_cast<uint4*>(sf_tile)[t] = reinterpret_cast<const uint4*>(sf_smem)[t];
-}
-
 struct QuantLaunch {
   const __nv_bfloat16 *q, *k, *v;
   int64_t q_sb, q_sh, q_sn, k_sb, k_sh, k_sn, v_sb, v_sh, v_sn;
@@ -144,6 +109,8 @@ struct QuantLaunch {
   __nv_bfloat16* qm;                     // [B,Hq,Tq,D] (mode 1)
   int q_blocks, k_blocks, v_blocks;      // CTAs per role
   const int *cu_q, *cu_k;                // variable-length batches (else null)
+  float* q_dot_km;                       // optional fp32 [B,Hq,Nq]: raw q . K channel mean of the row's kv head
+  const __nv_bfloat16* km_for_q;         //   (the term K smoothing removes from every score of the row)
 };
 
 template <int D>
@@ -174,6 +141,25 @@ __global__ void __launch_bounds__(kThreads) quant_qkv_kernel(const QuantLaunch P
     for (int p = 0; p < NP; ++p) {
       const int n = tile * kTile + p * RPP + rl;
       w[p] = n < N ? *reinterpret_cast<const uint4*>(src + (int64_t)n * sn + c * 8) : make_uint4(0, 0, 0, 0);
+    }
+    if (is_q && P.q_dot_km != nullptr) {
+      // q . km in fp32 from the raw rows: what K smoothing took out of every score of the row; the attention
+      // kernel adds sm_scale times it to the log-sum-exp (the pattern of sageattention/core.py:993-994)
+      const int hkv = h / (P.Hq / P.Hkv);
+      const uint4 m = *reinterpret_cast<const uint4*>(P.km_for_q + ((int64_t)b * P.Hkv + hkv) * D + c * 8);
+      const float kmv[8] = {bf16_lo(m.x), bf16_hi(m.x), bf16_lo(m.y), bf16_hi(m.y),
+                            bf16_lo(m.z), bf16_hi(m.z), bf16_lo(m.w), bf16_hi(m.w)};
+#pragma unroll
+      for (int p = 0; p < NP; ++p) {
+        float d = bf16_lo(w[p].x) * kmv[0];
+        d = fmaf(bf16_hi(w[p].x), kmv[1], d); d = fmaf(bf16_lo(w[p].y), kmv[2], d); d = fmaf(bf16_hi(w[p].y), kmv[3], d);
+        d = fmaf(bf16_lo(w[p].z), kmv[4], d); d = fmaf(bf16_hi(w[p].z), kmv[5], d); d = fmaf(bf16_lo(w[p].w), kmv[6], d);
+        d = fmaf(bf16_hi(w[p].w), kmv[7], d);
+#pragma unroll
+        for (int o = 1; o < CH; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        const int n = tile * kTile + p * RPP + rl;
+        if (c == 0 && n < N) P.q_dot_km[(int64_t)bh * P.Nq + n] = d;
+      }
     }
     float mean[8];
     bool subtract = true;
@@ -370,6 +356,8 @@ cudaError_t launch_quant_qkv(const QuantArgs& a, cudaStream_t stream) {
   P.vt_codes = (uint8_t*)a.vt_codes; P.vt_sf = (uint8_t*)a.vt_sf;
   P.qm = (__nv_bfloat16*)a.qm;
   P.cu_q = a.cu_q; P.cu_k = a.cu_k;
+  P.q_dot_km = (a.q_dot_km != nullptr && a.km != nullptr && a.cu_q == nullptr) ? (float*)a.q_dot_km : nullptr;
+  P.km_for_q = (const __nv_bfloat16*)a.km;
   P.q_blocks = a.q ? a.B * a.Hq * P.Tq : 0;
   P.k_blocks = a.k ? a.B * a.Hkv * P.Tk : 0;
   const int tpb = a.D == 128 ? 1 : 2;
