@@ -404,6 +404,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="dit", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="only the device-timed steps (for profiling): no end-to-end leg, copy rates, reference "
+                         "quantisation timing, FP4 peak measurement, Ulysses leg or CPU baseline")
     ap.add_argument("--sweep", action="store_true",
                     help="kernel-only TOPS over B=4 H=32, D in {64,128}, N = 1K..32K, causal and not (one JSON line per point)")
     args = ap.parse_args()
@@ -472,6 +475,17 @@ def main():
     total_ms, quant_ms, attn_ms = t.tolist()
     ms_per_step = total_ms / args.steps
     value = world * flops / (ms_per_step * 1e-3) / 1e12
+
+    if args.kernel_only:
+        if rank == 0:
+            print(json.dumps({"metric": "attention_tops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+                              "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+                              "config": {"workload": args.workload},
+                              "kernel_only": {"attention_ms": attn_ms, "preprocess_ms": quant_ms,
+                                              "attention_tops": flops / (attn_ms * 1e-3) / 1e12}}), flush=True)
+        if dist:
+            dist.destroy_process_group()
+        return
 
     # end to end through the public operator with HOST buffers: pinned H2D of q,k,v and D2H of the output
     qh, kh, vh = (x.cpu().pin_memory() for x in (q, k, v))

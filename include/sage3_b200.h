@@ -102,6 +102,10 @@ typedef struct {
                                 sage3_read_device_status)                                            */
   float* q_dot_km;           /* out, optional fp32 [B,Hq,Nq]: raw q . km of the row's kv head (needs smooth_k;
                                 dense batches) - feed it to sage3_attn_args.lse_add                   */
+  int32_t head_dim_in;       /* 0 or shape.D: the rows of q, k, v have shape.D channels.  Otherwise a
+                                multiple of 8 below shape.D: the rows have only that many channels and
+                                the kernels treat the rest of the head dim as zero - the head-dim
+                                padding of sageattention/core.py:925-937 without a padded copy       */
 } sage3_quant_args;
 
 typedef struct {
@@ -119,6 +123,8 @@ typedef struct {
   const float* lse_add;      /* optional fp32 [B,Hq,Nq]: sm_scale * lse_add is added to the LSE - with
                                 sage3_quant_args.q_dot_km this undoes the shift K smoothing gives every
                                 score of a row (the pattern of sageattention/core.py:993-994)         */
+  int32_t out_head_dim;      /* 0 or shape.D: `out` rows have shape.D columns.  Otherwise a multiple of 8
+                                below shape.D: only that many columns are written (core.py:990)      */
 } sage3_attn_args;
 
 typedef struct {
@@ -137,6 +143,9 @@ typedef struct {
   size_t workspace_bytes;
   int32_t* device_status;    /* optional device int32 (see sage3_attn_args); NULL: one inside the
                                 workspace is used and cannot be read back by the caller              */
+  int32_t head_dim;          /* 0 or shape.D, else the real head dim of q, k, v and out (a multiple of 8
+                                below shape.D, see sage3_quant_args.head_dim_in); the default softmax
+                                scale is then head_dim^-0.5 (core.py:941)                            */
 } sage3_fwd_args;
 
 /* K-packing mode of the fork ("SageAttention4", api.py:122-177, 193-203): every 15 key tokens become 16 key

@@ -13,6 +13,7 @@ read-only reference checkout, with the reference's own nvcc flags
 nothing is copied into this repository and the output directory is git-ignored.
 
 Usage:  python oracle/build_ref.py [path-to-reference-checkout]
+The checkout is looked for at the argument, else at $SAGE_REFERENCE_ROOT, else at the default below.
 """
 import os
 import sys
@@ -23,8 +24,15 @@ OUT = HERE / "_ref"
 MODULE = "sage_ref_quant_cuda"
 
 
-def build(reference_root: str = "/root/reference", verbose: bool = False):
-    src = Path(reference_root) / "sageattention3_blackwell" / "sageattn4" / "quantization"
+DEFAULT_REFERENCE_ROOT = "/root/reference"
+
+
+def reference_root() -> str:
+    return os.environ.get("SAGE_REFERENCE_ROOT") or DEFAULT_REFERENCE_ROOT
+
+
+def build(reference_root_: str = "", verbose: bool = False):
+    src = Path(reference_root_ or reference_root()) / "sageattention3_blackwell" / "sageattn4" / "quantization"
     cu = src / "fp4_quantization_4d.cu"
     if not cu.exists():
         raise FileNotFoundError(f"reference quantization source not found: {cu}")
@@ -46,5 +54,4 @@ def build(reference_root: str = "/root/reference", verbose: bool = False):
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
-    print(build(root, verbose=True))
+    print(build(sys.argv[1] if len(sys.argv) > 1 else "", verbose=True))

@@ -39,7 +39,7 @@ class QuantArgs(C.Structure):
                 ("vt_codes", C.c_void_p), ("vt_sf", C.c_void_p),
                 ("qm", C.c_void_p), ("km", C.c_void_p), ("delta_s", C.c_void_p),
                 ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t), ("device_status", C.c_void_p),
-                ("q_dot_km", C.c_void_p)]
+                ("q_dot_km", C.c_void_p), ("head_dim_in", C.c_int32)]
 
 
 class AttnArgs(C.Structure):
@@ -50,7 +50,7 @@ class AttnArgs(C.Structure):
                 ("out", C.c_void_p), ("out_stride_b", C.c_int64), ("out_stride_h", C.c_int64),
                 ("out_stride_n", C.c_int64),
                 ("lse", C.c_void_p), ("sm_scale", C.c_float), ("is_causal", C.c_int32),
-                ("device_status", C.c_void_p), ("lse_add", C.c_void_p)]
+                ("device_status", C.c_void_p), ("lse_add", C.c_void_p), ("out_head_dim", C.c_int32)]
 
 
 class FwdArgs(C.Structure):
@@ -59,7 +59,8 @@ class FwdArgs(C.Structure):
                 ("out_stride_n", C.c_int64),
                 ("lse", C.c_void_p), ("km_out", C.c_void_p), ("sm_scale", C.c_float), ("is_causal", C.c_int32),
                 ("per_block_mean", C.c_int32), ("smooth_k", C.c_int32),
-                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("device_status", C.c_void_p)]
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("device_status", C.c_void_p),
+                ("head_dim", C.c_int32)]
 
 
 class PackArgs(C.Structure):

@@ -262,8 +262,10 @@ def sageattn3_blackwell(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tenso
     argument set of ``sageattn`` (``sageattention/core.py:79-88``).
 
     q ``[B,Hq,Nq,D]`` ("HND") or ``[B,Nq,Hq,D]`` ("NHD"), k/v likewise with ``Hkv`` heads
-    (``Hq % Hkv == 0``), bf16, D in {64, 128}.  Returns a tensor shaped like q (and the natural-log
-    LSE ``[B,Hq,Nq]`` when ``return_lse``).  Causal masking is bottom-right aligned when Nq != Nk.
+    (``Hq % Hkv == 0``), bf16, D <= 128 (head dims other than 64 and 128 are zero-padded to the next of the two,
+    ``sageattention/core.py:925-937``).  Returns a tensor shaped like q (and the natural-log LSE ``[B,Hq,Nq]`` of
+    ``sm_scale * q.k`` when ``return_lse``; ``-inf`` for rows that see no key).  Causal masking is bottom-right
+    aligned when Nq != Nk.
     """
     if attn_mask is not None:
         raise NotImplementedError("attn_mask is not supported (the reference ignores it as well)")
@@ -277,10 +279,26 @@ def sageattn3_blackwell(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tenso
     Bv, Hv, Nv, Dv, vsb, vsh, vsn = _as_bhnd_strides(v, tensor_layout)
     if not (B == Bk == Bv and D == Dk == Dv and Hkv == Hv and Nk == Nv):
         raise ValueError("q, k, v shapes do not match")
-    if D not in (64, 128):
-        raise ValueError(f"Unsupported Headdim {D}")                              # api.py:253-255
     if Hq % Hkv != 0:
         raise ValueError("num_qo_heads must be a multiple of num_kv_heads")
+    # head-dim padding of sageattention/core.py:925-937: below 64 -> 64, between 64 and 128 -> 128, zeros in the
+    # extra channels, default scale from the original head dim, output cut back (:990).  The kernels read rows of the
+    # original width and take the rest as zero, so nothing is copied - if the width is a multiple of 8 (16-byte
+    # loads); other widths are padded here first, as the reference does.
+    d_og = D
+    if D > 128:
+        raise ValueError(f"Unsupported head_dim: {D}")                            # core.py:937
+    if D not in (64, 128) and D % 8 != 0:
+        pad = (64 if D < 64 else 128) - D
+        if sm_scale is None:
+            sm_scale = D ** -0.5
+        q, k, v = (torch.nn.functional.pad(t, (0, pad)) for t in (q, k, v))
+        res = sageattn3_blackwell(q, k, v, tensor_layout=tensor_layout, is_causal=is_causal, sm_scale=sm_scale,
+                                  per_block_mean=per_block_mean, return_lse=return_lse, smooth_k=smooth_k,
+                                  check_status=check_status)
+        return (res[0][..., :d_og].contiguous(), res[1]) if return_lse else res[..., :d_og].contiguous()
+    if D not in (64, 128):
+        D = 64 if D < 64 else 128
     dev = q.device
     pbm = int(bool(per_block_mean))
     z = buffer_sizes(B, Hq, Hkv, Nq, Nk, D, pbm)
@@ -299,6 +317,7 @@ def sageattn3_blackwell(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tenso
     a.is_causal, a.per_block_mean, a.smooth_k = int(bool(is_causal)), pbm, int(bool(smooth_k))
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
     a.device_status = status.data_ptr()
+    a.head_dim = d_og if d_og != D else 0
     with torch.cuda.device(dev):
         _lib.check(lib.sage3_attention(C.byref(a), _stream_ptr(dev)), "sage3_attention")
         if check_status:

@@ -13,14 +13,15 @@
 //   O /= l, bf16                                      softmax_fused.h:156-173, fwd_epilogue.cu:103-147
 // Key tiles are visited from the last to the first as the reference does (fwd_mainloop.cu:575).
 //
-// Where this kernel departs from the reference's arithmetic (inside the parity tolerance, see the tests):
-// the reference keeps O in registers and multiplies it by 2^(m_old - m_new) after EVERY key tile; here O stays in
-// tensor memory, the P.V MMAs accumulate into it, and it is rescaled only when a row's maximum has grown by more
-// than 2^kLazyLog2 since the reference maximum was last set.  Until then P is computed against that (stale)
-// reference maximum; so that it still fits the E4M3 block scales, P is normalised to (0, 2688 / 2^kLazyLog2]
-// against the reference maximum instead of (0, 2688] against the true one.  Block scales are powers of two apart
-// from the reference's unless they fall below the E4M3 normal range (blocks whose maximum is under 2^-11.8 of the
-// row's reference maximum instead of 2^-14.8).
+// O lives in tensor memory and the P.V MMAs accumulate into it (the reference keeps O in registers and adds a
+// fresh product per key tile); like the reference it is multiplied by 2^((m_old - m_new) c) whenever a row's
+// maximum has moved - here in place in tensor memory, and only by the warps in which some row's maximum did move,
+// which after the first few key tiles of a long row is rare.  P, its block scales and the row sum are the
+// reference's value for value (kLazyLog2 = 0).  A build with kLazyLog2 > 0 rescales only after the maximum has
+// grown by more than 2^kLazyLog2 and normalises P to 2688 / 2^kLazyLog2 instead; the E4M3 rounding of the block
+// scales then falls differently than in the reference (same size of error, different realisation), which
+// measured 2.7-3.1 % relative L1 against the restatement of the reference - outside the 2 % parity bar - for a
+// gain of a few percent, so it is not the default.
 //
 // One persistent CTA per SM walks a static list of work items (round r: item r*grid + i, odd rounds in
 // reverse CTA order; causal items sorted by falling cost over all heads);
@@ -90,10 +91,18 @@ static_assert(256 * RegSplit<128>::softmax + 128 * RegSplit<128>::role <= kAttnT
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLog2Inv2688 = -11.392317422778762f;   // log2(1 / (448 * 6))  softmax_fused.h:33
 constexpr float kLog2Inv6 = -2.584962500721156f;       // log2(1 / 6)          softmax_fused.h:34
-// O in tensor memory is rescaled only when a row maximum has grown by more than this (log2 units of P) since
-// the row's reference maximum was set; P is normalised to 2688 / 2^kLazyLog2 at the reference maximum so that
-// it cannot exceed 2688 (block scale 448, the E4M3 maximum) before that happens
-constexpr float kLazyLog2 = 3.0f;
+// O in tensor memory is rescaled when a row maximum has grown by more than this (log2 units of P) since the row's
+// reference maximum was set; P is normalised to 2688 / 2^kLazyLog2 at the reference maximum so that it cannot
+// exceed 2688 (block scale 448, the E4M3 maximum) before that happens.  0 = the reference's arithmetic.
+#ifndef SAGE3_LAZY_LOG2
+#define SAGE3_LAZY_LOG2 0
+#endif
+constexpr float kLazyLog2 = (float)SAGE3_LAZY_LOG2;
+// The exponentials of the two softmax warpgroups take turns (see the kernel): 1 = on
+#ifndef SAGE3_EXP_TURNS
+#define SAGE3_EXP_TURNS 1
+#endif
+constexpr bool kExpTurns = SAGE3_EXP_TURNS != 0;
 constexpr float kLog2InvTop = kLog2Inv2688 + kLazyLog2;
 
 template <int D>
@@ -142,7 +151,8 @@ struct Bars {            // byte offsets inside the barrier block
   static constexpr int o_free = pv_done + 16;             // [2] the epilogue has read O_t out of tensor memory
   static constexpr int drain = o_free + 16;               // [2] the issuers' last commit when giving up
   static constexpr int epi = drain + 16;                  // [2] rendezvous of a softmax warpgroup around its output staging
-  static constexpr int tmem_slot = epi + 16;              // u32 written by tcgen05.alloc
+  static constexpr int exp_done = epi + 16;               // [2] warpgroup t has finished the exponentials of a key tile
+  static constexpr int tmem_slot = exp_done + 16;         // u32 written by tcgen05.alloc
   static constexpr int abort_flag = tmem_slot + 8;
   static constexpr int run_flag = abort_flag + 4;
 };
@@ -159,6 +169,7 @@ struct KParams {
   float scale_log2;      // sm_scale * log2(e)
   const float* lam;      // K-packing mode: lambda per key slot, fp32 [B,Hkv,Tk*128]; Nk is the packed length
   int Nk_log;            // number of key tokens (= Nk unless packed)
+  int d_out;             // columns the output rows really have (<= D, multiple of 8)
   bool slot_first;       // K-packing mode: the mean slot takes the first token's score instead of being masked
   bool o_token_first;    // output tensor map: coordinates (d, token, head, batch) or (d, head, token, batch)
 #if SAGE3_VARLEN_BUILD
@@ -405,6 +416,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       mbar_init(bars + Bars::pv_done + 8 * t, 1);          // tcgen05.commit
       mbar_init(bars + Bars::o_free + 8 * t, 128);
       mbar_init(bars + Bars::epi + 8 * t, 128);
+      mbar_init(bars + Bars::exp_done + 8 * t, 128);
     }
     for (int s = 0; s < kStages; ++s) {
       mbar_init(bars + Bars::k_full + 8 * s, 1);
@@ -668,6 +680,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       const uint32_t bar_pv = bars + Bars::pv_done + 8 * t;
       uint32_t sc = 0;                                           // key tiles processed so far by this warpgroup
       uint32_t ne = 0;                                           // epilogue rendezvous so far
+      uint32_t other_before = 0;                                 // key tiles of the OTHER warpgroup in earlier work items
       uint32_t g0 = 0;                                           // K/V stages the CTA used before this work item
       bool ok = true;
       for (int r = 0, w; ok && (w = work_at(r, total_work)) >= 0; ++r) {
@@ -675,6 +688,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         const int n_mine = wk.n_t[t];
         const uint32_t g_first = g0 + (uint32_t)(wk.n_max - n_mine);   // stage counter of this tile's first key tile
         g0 += (uint32_t)wk.n_max;
+        const uint32_t other_prev = other_before;                // (the turn-taking below counts from the item's start)
+        other_before += (uint32_t)wk.n_t[t ^ 1];
         const int qt = 2 * wk.pair + t;
         const int q0 = qt * kBlockM, qpos = q0 + row;
 #if SAGE3_VARLEN_BUILD
@@ -686,7 +701,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           // query tile that sees no key at all (causal, more queries than keys): zeros, like the
           // reference's store_zero (fwd_epilogue.cu:150-183); nothing if the tile does not exist
           if (SEQ_TILE_EXISTS && qpos < SEQ_NQ) {
-            for (int i = 0; i < D / 8; ++i) reinterpret_cast<uint4*>(orow)[i] = make_uint4(0, 0, 0, 0);
+            for (int i = 0; i < P.d_out / 8; ++i) reinterpret_cast<uint4*>(orow)[i] = make_uint4(0, 0, 0, 0);
             if (P.lse) P.lse[((int64_t)wk.b * P.Hq + wk.hq) * P.Nq + qpos] = -INFINITY;
           }
           continue;
@@ -785,9 +800,25 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           }
           // P^ and its scales of the previous key tile must have been consumed by its P.V MMAs
           if (sc > 0 && !(ok = wait_bar<false>(bar_pv, (sc - 1) & 1, abort_s, P.status, 31))) break;
+          if (kExpTurns) {
+            // The exponentials below keep the special-function unit busy for as long as they last, everything else
+            // in this loop does not use it.  Left alone the two warpgroups drift into doing their exponentials at
+            // the same time (each then at half speed, and the unit idles while both load scores and take maxima).
+            // So the exponential phases follow one fixed order - that of the Q.K^T MMAs: key tile by key tile,
+            // query tile 0 before query tile 1 - and a phase starts when its predecessor has finished; the other
+            // warpgroup spends that time on the parts that need no exponentials.  `need` = how many phases of the
+            // other warpgroup come before this one in that order (it cannot be more than one phase ahead of that,
+            // since its next phase comes after this one).
+            const int first_other = wk.n_max - wk.n_t[t ^ 1];    // the other tile's first iteration in this item
+            const int it_abs = wk.n_max - n_mine + it;           // this key tile's iteration index in the item
+            const int within = it_abs + t - first_other;         // t = 1 also follows tile 0 of the same iteration
+            const uint32_t need = other_prev + (uint32_t)min(max(within, 0), wk.n_t[t ^ 1]);
+            if (need > 0 && !(ok = wait_bar<false>(bars + Bars::exp_done + 8 * (t ^ 1), (need - 1) & 1, abort_s, P.status, 34))) break;
+          }
           sfp_row[0] = f32x2_to_e4m3x2(sb[0], sb[1]) | (f32x2_to_e4m3x2(sb[2], sb[3]) << 16);     // keys 0-63 of the tile
           sfp_row[128] = f32x2_to_e4m3x2(sb[4], sb[5]) | (f32x2_to_e4m3x2(sb[6], sb[7]) << 16);   // keys 64-127
           l += exp_quantise_store<kPacked>(s, c, neg_e, sb, p_row, swz, P.slot_first);
+          if (kExpTurns) mbar_arrive(bars + Bars::exp_done + 8 * t);
           // P^ written (and O_t rescaled if it had to be): hand the tile to the PV issuer
           tc_fence_before();
           fence_proxy_async_smem();
@@ -866,7 +897,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
               v.y = pack_bf16(__uint_as_float(o[8 * h + 2]) * inv, __uint_as_float(o[8 * h + 3]) * inv);
               v.z = pack_bf16(__uint_as_float(o[8 * h + 4]) * inv, __uint_as_float(o[8 * h + 5]) * inv);
               v.w = pack_bf16(__uint_as_float(o[8 * h + 6]) * inv, __uint_as_float(o[8 * h + 7]) * inv);
-              if (live) reinterpret_cast<uint4*>(orow)[2 * ch + h] = v;
+              if (live && (2 * ch + h) * 8 < P.d_out) reinterpret_cast<uint4*>(orow)[2 * ch + h] = v;
             }
           }
           tc_fence_before();
@@ -928,7 +959,7 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint32_t row_byte
 // Tensor-map strides must grow with the dimension, so tokens and heads are ordered by their stride ("HND": D, N,
 // H, B; "NHD": D, H, N, B); *n_dim tells the kernel which coordinate is the token.
 bool make_out_map(CUtensorMap* m, const void* base, int B, int H, int N, int D, int64_t sb, int64_t sh, int64_t sn,
-                  int* n_dim) {
+                  int* n_dim) {   // D = columns the rows really have: the 64-column boxes are clipped to it
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return false;
   // a dimension of extent 1 never advances; give it a stride that keeps the order valid
@@ -964,10 +995,11 @@ cudaError_t launch(const AttnArgs& a, cudaStream_t stream) {
   if (!make_map(&tk, a.k_codes, (uint64_t)a.B * a.Hkv * Tk * 128, D / 2, 128, swz)) return cudaErrorInvalidValue;
   if (!make_map(&tv, a.vt_codes, (uint64_t)a.B * a.Hkv * Tk * D, 64, D, CU_TENSOR_MAP_SWIZZLE_64B))
     return cudaErrorInvalidValue;
+  const int d_out = (a.d_out > 0 && a.d_out <= D) ? a.d_out : D;
   CUtensorMap to = tq;                       // only D=128 dense batches store through it
   int o_ndim = 1;
   if (!SAGE3_VARLEN_BUILD && D == 128 &&
-      !make_out_map(&to, a.out, a.B, a.Hq, a.Nq, D, a.o_sb, a.o_sh, a.o_sn, &o_ndim))
+      !make_out_map(&to, a.out, a.B, a.Hq, a.Nq, d_out, a.o_sb, a.o_sh, a.o_sn, &o_ndim))
     return cudaErrorInvalidValue;
   KParams P;
   P.q_sf = (const uint8_t*)a.q_sf; P.k_sf = (const uint8_t*)a.k_sf; P.vt_sf = (const uint8_t*)a.vt_sf;
@@ -978,6 +1010,7 @@ cudaError_t launch(const AttnArgs& a, cudaStream_t stream) {
   P.o_token_first = o_ndim == 1;
   P.lam = a.k_lambda;
   P.slot_first = kPacked && a.slot_first != 0;
+  P.d_out = d_out;
   // K-packing mode: Nk counts key slots; 16 slots hold 15 tokens, a partial group one slot more than its tokens
   P.Nk_log = kPacked ? (a.Nk / 16) * 15 + (a.Nk % 16 == 0 ? 0 : a.Nk % 16 - 1) : a.Nk;
 #if SAGE3_VARLEN_BUILD

@@ -30,6 +30,9 @@ inline int check_shape(const sage3_shape& s) {
   return SAGE3_OK;
 }
 
+// real head dim of the caller's rows: 0 means D; otherwise a multiple of 8 (128-bit loads) not above D
+inline bool head_dim_ok(int d, int D) { return d == 0 || (d > 0 && d <= D && d % 8 == 0); }
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 inline int check_tensor(const sage3_tensor& t) {
@@ -100,6 +103,7 @@ static int quant_qkv_impl(const sage3_quant_args* a, const int* cu_q, const int*
   if (a->v.ptr && (!a->vt_codes || !a->vt_sf)) return SAGE3_ERR_ARGUMENT;
   if (a->q.ptr && a->per_block_mean >= 0 && !a->qm) return SAGE3_ERR_ARGUMENT;
   if (a->per_block_mean < -1 || a->per_block_mean > 1) return SAGE3_ERR_ARGUMENT;
+  if (!head_dim_ok(a->head_dim_in, s.D)) return SAGE3_ERR_ARGUMENT;
 
   const void* km = nullptr;
   if (a->k.ptr && a->smooth_k) {
@@ -109,7 +113,7 @@ static int quant_qkv_impl(const sage3_quant_args* a, const int* cu_q, const int*
       if (!a->km || !a->scratch || !aligned16(a->scratch)) return SAGE3_ERR_ARGUMENT;
       if (a->scratch_bytes < sage3::quant_scratch_bytes(s.B, s.Hkv, s.Nk, s.D)) return SAGE3_ERR_ARGUMENT;
       cudaError_t e = sage3::launch_channel_mean(a->k.ptr, a->k.stride_b, a->k.stride_h, a->k.stride_n, s.B, s.Hkv,
-                                                 s.Nk, s.D, (float)s.Nk, a->scratch, a->km, stream, cu_k);
+                                                 s.Nk, s.D, (float)s.Nk, a->scratch, a->km, stream, cu_k, a->head_dim_in);
       if (e != cudaSuccess) return cuda_fail(e);
       km = a->km;
     }
@@ -122,7 +126,7 @@ static int quant_qkv_impl(const sage3_quant_args* a, const int* cu_q, const int*
         a->scratch_bytes < sage3::quant_scratch_bytes(s.B, s.Hq, s.Nq, s.D))
       return SAGE3_ERR_ARGUMENT;
     cudaError_t e = sage3::launch_channel_mean(a->q.ptr, a->q.stride_b, a->q.stride_h, a->q.stride_n, s.B, s.Hq, s.Nq,
-                                               s.D, (float)(Tq * 128), a->scratch, a->qm, stream);
+                                               s.D, (float)(Tq * 128), a->scratch, a->qm, stream, nullptr, a->head_dim_in);
     if (e != cudaSuccess) return cuda_fail(e);
   }
 
@@ -142,6 +146,7 @@ static int quant_qkv_impl(const sage3_quant_args* a, const int* cu_q, const int*
   q.q_codes = a->q_codes; q.q_sf = a->q_sf; q.k_codes = a->k_codes; q.k_sf = a->k_sf;
   q.vt_codes = a->vt_codes; q.vt_sf = a->vt_sf; q.qm = a->qm;
   q.cu_q = cu_q; q.cu_k = cu_k;
+  q.d_in = a->head_dim_in;
   if (a->q_dot_km != nullptr) {
     if (km == nullptr || cu_q != nullptr || !a->q.ptr) return SAGE3_ERR_ARGUMENT;
     q.q_dot_km = a->q_dot_km;
@@ -153,7 +158,7 @@ static int quant_qkv_impl(const sage3_quant_args* a, const int* cu_q, const int*
     sage3::DeltaSArgs d{};
     d.qm = a->qm; d.k = a->k.ptr; d.k_sb = a->k.stride_b; d.k_sh = a->k.stride_h; d.k_sn = a->k.stride_n;
     d.km = km; d.ds = a->delta_s; d.cu_k = cu_k;
-    d.k_codes = a->k_codes; d.k_sf = a->k_sf; d.status = a->device_status;
+    d.k_codes = a->k_codes; d.k_sf = a->k_sf; d.status = a->device_status; d.d_in = a->head_dim_in;
     d.B = s.B; d.Hq = s.Hq; d.Hkv = s.Hkv; d.Tq = a->per_block_mean == 1 ? Tq : 1; d.Nk = s.Nk; d.D = s.D;
     e = sage3::launch_delta_s(d, stream);
     if (e != cudaSuccess) return cuda_fail(e);
@@ -177,6 +182,7 @@ static int attn_fwd_impl(const sage3_attn_args* a, const float* k_lambda, const 
   const int Tq = (s.Nq + 127) / 128;
   if (a->delta_s && a->delta_s_rows != 1 && a->delta_s_rows != Tq) return SAGE3_ERR_ARGUMENT;
   if (!(a->sm_scale > 0.f)) return SAGE3_ERR_ARGUMENT;          // the row maximum is tracked in raw score units
+  if (!head_dim_ok(a->out_head_dim, s.D)) return SAGE3_ERR_ARGUMENT;
   cudaStream_t stream = (cudaStream_t)stream_;
   cudaError_t e = cudaSuccess;
   if (zero_status) {
@@ -192,6 +198,7 @@ static int attn_fwd_impl(const sage3_attn_args* a, const float* k_lambda, const 
   k.sm_scale = a->sm_scale; k.causal = a->is_causal;
   k.k_lambda = k_lambda;
   k.slot_first = slot_first;
+  k.d_out = a->out_head_dim;
   k.cu_q = cu_q; k.cu_k = cu_k;
   e = (cu_q != nullptr || cu_k != nullptr) ? sage3::launch_attn_fwd_varlen(k, stream) : sage3::launch_attn_fwd(k, stream);
   if (e != cudaSuccess) return cuda_fail(e);
@@ -266,7 +273,10 @@ int sage3_attention(const sage3_fwd_args* a, void* stream) {
   int32_t* status = reinterpret_cast<int32_t*>(take(4));
   if (a->device_status) status = a->device_status;
   if (a->lse && a->smooth_k) q.q_dot_km = qk;
-  const float sm_scale = a->sm_scale > 0.f ? a->sm_scale : 1.0f / sqrtf((float)a->shape.D);
+  if (!head_dim_ok(a->head_dim, a->shape.D)) return SAGE3_ERR_ARGUMENT;
+  const int d_real = a->head_dim > 0 ? a->head_dim : a->shape.D;
+  const float sm_scale = a->sm_scale > 0.f ? a->sm_scale : 1.0f / sqrtf((float)d_real);
+  q.head_dim_in = a->head_dim;
   q.delta_s = a->per_block_mean >= 0 ? ds : nullptr;
   // one status word for the whole call: zeroed here, the preprocessing kernels and the attention kernel report in it
   q.device_status = status;
@@ -288,6 +298,7 @@ int sage3_attention(const sage3_fwd_args* a, void* stream) {
   t.out = a->out; t.out_stride_b = a->out_stride_b; t.out_stride_h = a->out_stride_h; t.out_stride_n = a->out_stride_n;
   t.lse = a->lse; t.sm_scale = sm_scale; t.is_causal = a->is_causal; t.device_status = status;
   t.lse_add = q.q_dot_km;
+  t.out_head_dim = a->head_dim;
   return attn_fwd_impl(&t, nullptr, nullptr, nullptr, stream, 0, /*zero_status=*/false);
 }
 

@@ -36,6 +36,7 @@ struct KDsParams {
   int* status;                                         // optional device status word
   int Hq, Hkv, Tq, Tk, Nk;
   const int* cu_k;
+  int d_in;                                            // channels the K rows really have; the rest are zero
 };
 
 template <int D>
@@ -70,7 +71,7 @@ __global__ void __launch_bounds__(kThreads, 2) k_quant_delta_s_kernel(const KDsP
 #pragma unroll
   for (int p = 0; p < NP; ++p) {                       // all loads in flight before the first use
     const int n = tile * kTile + p * RPP + rl;
-    w[p] = n < Nk ? *reinterpret_cast<const uint4*>(src + (int64_t)n * P.k_sn) : make_uint4(0, 0, 0, 0);
+    w[p] = (n < Nk && c * 8 < P.d_in) ? *reinterpret_cast<const uint4*>(src + (int64_t)n * P.k_sn) : make_uint4(0, 0, 0, 0);
   }
   if (P.km != nullptr) {
     const uint4 m = *reinterpret_cast<const uint4*>(P.km + (int64_t)bh * D + c * 8);
@@ -186,6 +187,7 @@ cudaError_t launch_delta_s(const DeltaSArgs& a, cudaStream_t stream) {
   P.ds = (__nv_bfloat16*)a.ds; P.status = a.status;
   P.Hq = a.Hq; P.Hkv = a.Hkv; P.Tq = a.Tq; P.Nk = a.Nk; P.Tk = (a.Nk + 127) / 128;
   P.cu_k = a.cu_k;
+  P.d_in = (a.d_in > 0 && a.d_in <= a.D) ? a.d_in : a.D;
   dim3 grid(P.Tk, a.B * a.Hkv);
   const int smem = 2 * (a.D / 8) * (int)kChunk + 2048 + 16;
   // per device and cheap, so set on every call rather than cached per process

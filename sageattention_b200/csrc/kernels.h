@@ -20,12 +20,14 @@ struct QuantArgs {
   // tensors (then *_sb is ignored and Nq / Nk are the LONGEST sequence, which sizes the output layouts)
   const int* cu_q = nullptr;
   const int* cu_k = nullptr;
+  int d_in = 0;                           // channels the input rows really have (0 = D; <= D, multiple of 8): the
+                                          // kernels read only those and treat the rest of the head dim as zero
 };
 
 size_t quant_scratch_bytes(int B, int H, int N, int D);
 cudaError_t launch_channel_mean(const void* x, int64_t sb, int64_t sh, int64_t sn, int B, int H, int N, int D,
                                 float divisor, void* scratch, void* mean_out, cudaStream_t stream,
-                                const int* cu = nullptr);
+                                const int* cu = nullptr, int d_in = 0);
 cudaError_t launch_quant_qkv(const QuantArgs& a, cudaStream_t stream);
 cudaError_t launch_channel_mean_static(const void* x, int64_t sb, int64_t sh, int64_t sn, int B, int H, int N, int D,
                                        float divisor, void* mean_out, cudaStream_t stream, bool* too_large);
@@ -53,6 +55,7 @@ struct DeltaSArgs {
   void* k_codes = nullptr;                // when given, the kernel also writes the NVFP4 codes and scales of the
   void* k_sf = nullptr;                   //   smoothed K tile it holds (the K role of the quantisation kernel)
   int* status = nullptr;                  // optional device status word for the kernel's bounded wait
+  int d_in = 0;                           // as in QuantArgs
 };
 cudaError_t launch_delta_s(const DeltaSArgs& a, cudaStream_t stream);
 
@@ -70,6 +73,7 @@ struct AttnArgs {
   int causal;
   const float* k_lambda;                  // K-packing mode: fp32 [B,Hkv,Tk*128]; Nk is then the packed length
   int slot_first = 0;                     // K-packing mode: mean slot = first token's score (else masked)
+  int d_out = 0;                          // columns the output rows really have (0 = D; <= D, multiple of 8)
   const int* cu_q = nullptr;              // variable-length batches, see QuantArgs; out is then [tokens, Hq, D]
   const int* cu_k = nullptr;
 };

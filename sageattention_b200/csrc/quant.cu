@@ -39,7 +39,7 @@ template <int D>
 __global__ void __launch_bounds__(kThreads) channel_mean_kernel(
     const __nv_bfloat16* __restrict__ x, int64_t sb, int64_t sh, int64_t sn, int H, int N,
     int chunk_tokens, float divisor, float* __restrict__ partial, unsigned int* __restrict__ counters,
-    __nv_bfloat16* __restrict__ mean_out, const int* __restrict__ cu) {
+    __nv_bfloat16* __restrict__ mean_out, const int* __restrict__ cu, int d_in) {
   constexpr int CH = D / 8;              // 16-byte chunks per row
   constexpr int RPP = kThreads / CH;     // rows per pass
   __shared__ float red[RPP][D];
@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(kThreads) channel_mean_kernel(
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       int nn = n + u * RPP;
-      v[u] = nn < n1 ? *reinterpret_cast<const uint4*>(base + (int64_t)nn * sn) : make_uint4(0, 0, 0, 0);
+      v[u] = (nn < n1 && c * 8 < d_in) ? *reinterpret_cast<const uint4*>(base + (int64_t)nn * sn) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
@@ -109,6 +109,7 @@ struct QuantLaunch {
   __nv_bfloat16* qm;                     // [B,Hq,Tq,D] (mode 1)
   int q_blocks, k_blocks, v_blocks;      // CTAs per role
   const int *cu_q, *cu_k;                // variable-length batches (else null)
+  int d_in;                              // channels the input rows really have (<= D, multiple of 8); the rest are zero
   float* q_dot_km;                       // optional fp32 [B,Hq,Nq]: raw q . K channel mean of the row's kv head
   const __nv_bfloat16* km_for_q;         //   (the term K smoothing removes from every score of the row)
 };
@@ -140,7 +141,7 @@ __global__ void __launch_bounds__(kThreads) quant_qkv_kernel(const QuantLaunch P
 #pragma unroll
     for (int p = 0; p < NP; ++p) {
       const int n = tile * kTile + p * RPP + rl;
-      w[p] = n < N ? *reinterpret_cast<const uint4*>(src + (int64_t)n * sn + c * 8) : make_uint4(0, 0, 0, 0);
+      w[p] = (n < N && c * 8 < P.d_in) ? *reinterpret_cast<const uint4*>(src + (int64_t)n * sn + c * 8) : make_uint4(0, 0, 0, 0);
     }
     if (is_q && P.q_dot_km != nullptr) {
       // q . km in fp32 from the raw rows: what K smoothing took out of every score of the row; the attention
@@ -265,7 +266,7 @@ __global__ void __launch_bounds__(kThreads) quant_qkv_kernel(const QuantLaunch P
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const int n = tile * kTile + blk * 16 + i;
-      x[i] = n < Nv ? *reinterpret_cast<const uint2*>(src + (int64_t)n * P.v_sn) : make_uint2(0, 0);
+      x[i] = (n < Nv && c4 * 4 < P.d_in) ? *reinterpret_cast<const uint2*>(src + (int64_t)n * P.v_sn) : make_uint2(0, 0);
     }
     uint8_t* codes = P.vt_codes + gt * (D * 64);
 #pragma unroll
@@ -321,7 +322,9 @@ size_t quant_scratch_bytes(int B, int H, int N, int D) {
 }
 
 cudaError_t launch_channel_mean(const void* x, int64_t sb, int64_t sh, int64_t sn, int B, int H, int N, int D,
-                                float divisor, void* scratch, void* mean_out, cudaStream_t stream, const int* cu) {
+                                float divisor, void* scratch, void* mean_out, cudaStream_t stream, const int* cu,
+                                int d_in) {
+  if (d_in <= 0 || d_in > D) d_in = D;
   int chunk = pick_chunk_tokens(N, B * H);
   int nchunks = (N + chunk - 1) / chunk;
   size_t part = (size_t)B * H * nchunks * D * sizeof(float);
@@ -333,10 +336,10 @@ cudaError_t launch_channel_mean(const void* x, int64_t sb, int64_t sh, int64_t s
   dim3 grid(nchunks, B * H);
   if (D == 128)
     channel_mean_kernel<128><<<grid, kThreads, 0, stream>>>((const __nv_bfloat16*)x, sb, sh, sn, H, N, chunk, divisor,
-                                                            partial, counters, (__nv_bfloat16*)mean_out, cu);
+                                                            partial, counters, (__nv_bfloat16*)mean_out, cu, d_in);
   else
     channel_mean_kernel<64><<<grid, kThreads, 0, stream>>>((const __nv_bfloat16*)x, sb, sh, sn, H, N, chunk, divisor,
-                                                           partial, counters, (__nv_bfloat16*)mean_out, cu);
+                                                           partial, counters, (__nv_bfloat16*)mean_out, cu, d_in);
   return cudaGetLastError();
 }
 
@@ -356,6 +359,7 @@ cudaError_t launch_quant_qkv(const QuantArgs& a, cudaStream_t stream) {
   P.vt_codes = (uint8_t*)a.vt_codes; P.vt_sf = (uint8_t*)a.vt_sf;
   P.qm = (__nv_bfloat16*)a.qm;
   P.cu_q = a.cu_q; P.cu_k = a.cu_k;
+  P.d_in = (a.d_in > 0 && a.d_in <= a.D) ? a.d_in : a.D;
   P.q_dot_km = (a.q_dot_km != nullptr && a.km != nullptr && a.cu_q == nullptr) ? (float*)a.q_dot_km : nullptr;
   P.km_for_q = (const __nv_bfloat16*)a.km;
   P.q_blocks = a.q ? a.B * a.Hq * P.Tq : 0;
@@ -417,10 +421,10 @@ cudaError_t launch_channel_mean_static(const void* x, int64_t sb, int64_t sh, in
   dim3 grid(nchunks, B * H);
   if (D == 128)
     channel_mean_kernel<128><<<grid, kThreads, 0, stream>>>((const __nv_bfloat16*)x, sb, sh, sn, H, N, chunk, divisor,
-                                                            partial, counters, (__nv_bfloat16*)mean_out, nullptr);
+                                                            partial, counters, (__nv_bfloat16*)mean_out, nullptr, D);
   else
     channel_mean_kernel<64><<<grid, kThreads, 0, stream>>>((const __nv_bfloat16*)x, sb, sh, sn, H, N, chunk, divisor,
-                                                           partial, counters, (__nv_bfloat16*)mean_out, nullptr);
+                                                           partial, counters, (__nv_bfloat16*)mean_out, nullptr, D);
   return cudaGetLastError();
 }
 

@@ -270,3 +270,20 @@ def test_host_tensor_entry_point_batched_is_copy_bound_not_stride_bound():
     got = sa.sageattn_from_host(q.pin_memory(), k.pin_memory(), v.pin_memory(), head_chunks=4)
     torch.cuda.synchronize()
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("D,layout,causal", [(96, "HND", False), (40, "NHD", True), (72, "HND", True), (100, "HND", False)])
+def test_head_dims_other_than_64_and_128_are_zero_padded(D, layout, causal):
+    """sageattention/core.py:925-937, :990: D < 64 -> 64, 64 < D < 128 -> 128 with zero channels, default scale from
+    the original D, output cut back.  Multiples of 8 are padded inside the kernels (no copy), others in PyTorch."""
+    B, Hq, Hkv, N = 1, 4, 2, 300
+    q, k, v = U.make_qkv(B, Hq, Hkv, N, N, D, seed=D, layout=layout, device=DEV)
+    out, lse = sa.sageattn(q, k, v, tensor_layout=layout, is_causal=causal, return_lse=True, check_status=True)
+    assert out.shape == q.shape
+    Dp = 64 if D < 64 else 128
+    hnd = (lambda t: t.transpose(1, 2)) if layout == "NHD" else (lambda t: t)
+    qp, kp, vp = (torch.nn.functional.pad(hnd(t).cpu(), (0, Dp - D)).contiguous() for t in (q, k, v))
+    emu, emu_lse = sage3.sageattn3_emulated(qp, kp, vp, is_causal=causal, sm_scale=D ** -0.5, return_lse=True)
+    cos, l1 = sage3.accuracy(hnd(out).float().cpu(), emu[..., :D].float())
+    assert cos >= COS_MIN and l1 <= REL_L1_MAX, (cos, l1)
+    assert torch.allclose(lse.cpu(), emu_lse, atol=5e-3, rtol=1e-4)

@@ -77,7 +77,11 @@ def _check_all(z, out, lse, sm_scale, causal):
     for b in range(B):
         for h in range(Hq):
             for r0 in range(0, Nq, 256):
-                cos, l1 = sage3.accuracy(got[b, h, r0:r0 + 256], ref[b, h, r0:r0 + 256])
+                g_, r_ = got[b, h, r0:r0 + 256], ref[b, h, r0:r0 + 256]
+                if float(r_.abs().max()) == 0.0:                  # causal rows that see no key: zeros on both sides
+                    assert float(g_.abs().max()) == 0.0, (b, h, r0)
+                    continue
+                cos, l1 = sage3.accuracy(g_, r_)
                 assert cos >= COS_MIN and l1 <= 2 * REL_L1_MAX, (b, h, r0, cos, l1)
     if lse is not None:
         fin = torch.isfinite(want_lse)

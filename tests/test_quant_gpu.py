@@ -152,8 +152,9 @@ def test_bad_arguments_are_rejected():
     q, k, v = U.make_qkv(1, 2, 2, 128, 128, 128, device=DEV)
     with pytest.raises(AssertionError):
         sa.quantize_qkv(q.half(), k.half(), v.half())
+    big = torch.zeros(1, 2, 128, 136, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(ValueError):
-        sa.sageattn3_blackwell(q[..., :96].contiguous(), k[..., :96].contiguous(), v[..., :96].contiguous())
+        sa.sageattn3_blackwell(big, big, big)                   # head dims above 128: core.py:937
     with pytest.raises(ValueError):
         sa.sageattn3_blackwell(q, k, v, tensor_layout="XYZ")
     q3 = torch.cat([q, q], dim=1)[:, :3].contiguous()      # 3 query heads over 2 kv heads

@@ -47,4 +47,7 @@ def test_static_scratch_rejects_oversized_problems():
     big = _lib.Shape(64, 64, 64, 128, 128, 128)          # 4096 heads > 2048 counters; rejected before any launch
     assert lib.sage3_k_mean_static(C.byref(big), C.byref(kt), out.data_ptr(), None) == _lib.ERR_TOO_LARGE
     assert b"fixed scratch" in lib.sage3_status_string(_lib.ERR_TOO_LARGE)
+    # the other limit: few enough heads (64 <= 2048) but too many partial rows - 64 heads x 49 chunks of 4096 tokens
+    rows = _lib.Shape(1, 64, 64, 128, 200000, 128)
+    assert lib.sage3_k_mean_static(C.byref(rows), C.byref(kt), out.data_ptr(), None) == _lib.ERR_TOO_LARGE
     assert lib.sage3_k_mean_static(None, C.byref(kt), out.data_ptr(), None) == _lib.ERR_ARGUMENT
