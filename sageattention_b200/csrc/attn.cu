@@ -85,7 +85,11 @@ constexpr int kAttnThreads = 384;
 // it would block forever, so the split is checked here.  kLaunchRegs is what the compiler allocates under
 // __launch_bounds__(384, 1).
 constexpr int kLaunchRegs = 168;
-template <int D> struct RegSplit { static constexpr int softmax = 224, role = 56; };
+#ifndef SAGE3_REGS_SOFTMAX
+#define SAGE3_REGS_SOFTMAX 224
+#define SAGE3_REGS_ROLE 56
+#endif
+template <int D> struct RegSplit { static constexpr int softmax = SAGE3_REGS_SOFTMAX, role = SAGE3_REGS_ROLE; };
 static_assert(256 * RegSplit<128>::softmax + 128 * RegSplit<128>::role <= kAttnThreads * kLaunchRegs,
               "setmaxnreg split exceeds the CTA's register pool");
 constexpr float kLog2e = 1.4426950408889634f;
@@ -98,11 +102,6 @@ constexpr float kLog2Inv6 = -2.584962500721156f;       // log2(1 / 6)          s
 #define SAGE3_LAZY_LOG2 0
 #endif
 constexpr float kLazyLog2 = (float)SAGE3_LAZY_LOG2;
-// The exponentials of the two softmax warpgroups take turns (see the kernel): 1 = on
-#ifndef SAGE3_EXP_TURNS
-#define SAGE3_EXP_TURNS 1
-#endif
-constexpr bool kExpTurns = SAGE3_EXP_TURNS != 0;
 constexpr float kLog2InvTop = kLog2Inv2688 + kLazyLog2;
 
 template <int D>
@@ -151,8 +150,7 @@ struct Bars {            // byte offsets inside the barrier block
   static constexpr int o_free = pv_done + 16;             // [2] the epilogue has read O_t out of tensor memory
   static constexpr int drain = o_free + 16;               // [2] the issuers' last commit when giving up
   static constexpr int epi = drain + 16;                  // [2] rendezvous of a softmax warpgroup around its output staging
-  static constexpr int exp_done = epi + 16;               // [2] warpgroup t has finished the exponentials of a key tile
-  static constexpr int tmem_slot = exp_done + 16;         // u32 written by tcgen05.alloc
+  static constexpr int tmem_slot = epi + 16;              // u32 written by tcgen05.alloc
   static constexpr int abort_flag = tmem_slot + 8;
   static constexpr int run_flag = abort_flag + 4;
 };
@@ -234,31 +232,6 @@ __device__ __forceinline__ void load_scores(const uint32_t tm_S, uint32_t (&s)[1
   tmem_wait_ld();
 }
 
-// 2^x for a pair of exponents on the FMA pipe instead of the special-function unit (which, at 16 results per
-// clock and SM, is what bounds this kernel): x = n + f with n = round(x), 2^f on [-0.5, 0.5] by a cubic (maximum
-// relative error 7.5e-5, far below the E2M1 rounding of the result), 2^n by adding n to the exponent field.
-// x must be <= 127; anything below -125 (masked scores are -inf) gives 2^-125, which rounds to code 0.
-__device__ __forceinline__ float2 exp2_fma_pipe(float2 x) {
-  const float2 magic = make_float2(12582912.f, 12582912.f);           // 1.5 * 2^23: the sum's low mantissa bits hold n
-  x.x = fmaxf(x.x, -125.f);
-  x.y = fmaxf(x.y, -125.f);
-  const float2 t = fadd2(x, magic);
-  const float2 n = fadd2(t, make_float2(-12582912.f, -12582912.f));
-  const float2 f = ffma2(n, make_float2(-1.f, -1.f), x);
-  float2 p = ffma2(f, make_float2(0.05517132f, 0.05517132f), make_float2(0.24261055f, 0.24261055f));
-  p = ffma2(p, f, make_float2(0.69326099f, 0.69326099f));
-  p = ffma2(p, f, make_float2(0.99992811f, 0.99992811f));
-  p.x = __uint_as_float(__float_as_uint(p.x) + (__float_as_uint(t.x) << 23));
-  p.y = __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(t.y) << 23));
-  return p;
-}
-
-// How many of the 8 element pairs of every 16-key block take the FMA-pipe exponential (the rest use ex2.approx).
-#ifndef SAGE3_POLY_PAIRS
-#define SAGE3_POLY_PAIRS 0
-#endif
-constexpr int kPolyPairs = SAGE3_POLY_PAIRS;
-
 // P / blockscale = 2^(s*c - (bm*c + log2(1/6))) in [0, 6] -> E2M1 codes into the swizzled P^ tile (64 bytes per
 // row); returns the row sum of the unquantised P = sum over blocks of (sum of P/blockscale) * blockscale
 // (softmax_fused.h:135-153).  neg_e[b] = -(bm_b*c + log2(1/6)), sb[b] = the block's unrounded scale.
@@ -279,14 +252,8 @@ __device__ __forceinline__ float exp_quantise_store(const uint32_t (&s)[128], co
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       e[i] = ffma2(make_float2(__uint_as_float(s[16 * blk + 2 * i]), __uint_as_float(s[16 * blk + 2 * i + 1])), c2, nb2);
-      // the pairs that take the FMA pipe are spread over the block (and shifted from block to block) so that both
-      // pipes have work at any time
-      if (((i + blk) & 7) < kPolyPairs) {
-        e[i] = exp2_fma_pipe(e[i]);
-      } else {
-        e[i].x = ex2_approx(e[i].x);
-        e[i].y = ex2_approx(e[i].y);
-      }
+      e[i].x = ex2_approx(e[i].x);
+      e[i].y = ex2_approx(e[i].y);
     }
     const float2 s4 = fadd2(fadd2(fadd2(e[0], e[1]), fadd2(e[2], e[3])), fadd2(fadd2(e[4], e[5]), fadd2(e[6], e[7])));
     float bsum = s4.x + s4.y;
@@ -416,7 +383,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       mbar_init(bars + Bars::pv_done + 8 * t, 1);          // tcgen05.commit
       mbar_init(bars + Bars::o_free + 8 * t, 128);
       mbar_init(bars + Bars::epi + 8 * t, 128);
-      mbar_init(bars + Bars::exp_done + 8 * t, 128);
     }
     for (int s = 0; s < kStages; ++s) {
       mbar_init(bars + Bars::k_full + 8 * s, 1);
@@ -680,7 +646,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       const uint32_t bar_pv = bars + Bars::pv_done + 8 * t;
       uint32_t sc = 0;                                           // key tiles processed so far by this warpgroup
       uint32_t ne = 0;                                           // epilogue rendezvous so far
-      uint32_t other_before = 0;                                 // key tiles of the OTHER warpgroup in earlier work items
       uint32_t g0 = 0;                                           // K/V stages the CTA used before this work item
       bool ok = true;
       for (int r = 0, w; ok && (w = work_at(r, total_work)) >= 0; ++r) {
@@ -688,8 +653,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         const int n_mine = wk.n_t[t];
         const uint32_t g_first = g0 + (uint32_t)(wk.n_max - n_mine);   // stage counter of this tile's first key tile
         g0 += (uint32_t)wk.n_max;
-        const uint32_t other_prev = other_before;                // (the turn-taking below counts from the item's start)
-        other_before += (uint32_t)wk.n_t[t ^ 1];
         const int qt = 2 * wk.pair + t;
         const int q0 = qt * kBlockM, qpos = q0 + row;
 #if SAGE3_VARLEN_BUILD
@@ -759,34 +722,21 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
 #pragma unroll
           for (int blk = 0; blk < 8; ++blk) bm[blk] = max16(&s[16 * blk]);
           const float m_loc = fmax3(fmax3(bm[0], bm[1], bm[2]), fmax3(bm[3], bm[4], bm[5]), fmaxf(bm[6], bm[7]));
+          // O_t *= alpha for the rows whose reference maximum moves, in place in tensor memory - but only after this
+          // tile's exponentials (below): by then the P.V of the previous key tile, which must land first, has long
+          // finished, so nothing waits for it.  Warps in which no row's maximum moved skip the pass.
+          float alpha = 1.0f;
+          bool rescale = false;
           if (it == 0) {
             m_ref = m_loc;                                       // O_t is overwritten by this tile's P.V
           } else {
             // (-inf) - (-inf) = NaN compares false: a row that has seen no key yet and sees none now stays put
             const bool grow = (m_loc - m_ref) * c > kLazyLog2;
-            if (__any_sync(0xffffffffu, grow)) {
-              // O_t *= 2^((m_ref - m_loc) c) for the rows that need it, in place in tensor memory; the P.V of the
-              // previous key tile must have landed first.  Rare: the maximum has to grow by a factor 2^kLazyLog2.
-              if (!(ok = wait_bar<false>(bar_pv, (sc - 1) & 1, abort_s, P.status, 32))) break;
-              tc_fence_after();
-              const float alpha = grow ? ex2_approx((m_ref - m_loc) * c) : 1.0f;
-              if (grow) m_ref = m_loc;
+            rescale = __any_sync(0xffffffffu, grow);
+            if (grow) {
+              alpha = ex2_approx((m_ref - m_loc) * c);
+              m_ref = m_loc;
               l *= alpha;
-              const float2 al2 = make_float2(alpha, alpha);
-#pragma unroll
-              for (int ch = 0; ch < D / 16; ++ch) {
-                uint32_t o[16];
-                tmem_ld16(tm_O + ch * 16, o);
-                tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  const float2 x = ffma2(make_float2(__uint_as_float(o[2 * i]), __uint_as_float(o[2 * i + 1])), al2,
-                                         make_float2(0.f, 0.f));
-                  o[2 * i] = __float_as_uint(x.x); o[2 * i + 1] = __float_as_uint(x.y);
-                }
-                tmem_st16(tm_O + ch * 16, o);
-              }
-              tmem_wait_st();
             }
           }
           const float m_fin = (m_ref == -INFINITY) ? 0.f : m_ref;
@@ -800,25 +750,29 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           }
           // P^ and its scales of the previous key tile must have been consumed by its P.V MMAs
           if (sc > 0 && !(ok = wait_bar<false>(bar_pv, (sc - 1) & 1, abort_s, P.status, 31))) break;
-          if (kExpTurns) {
-            // The exponentials below keep the special-function unit busy for as long as they last, everything else
-            // in this loop does not use it.  Left alone the two warpgroups drift into doing their exponentials at
-            // the same time (each then at half speed, and the unit idles while both load scores and take maxima).
-            // So the exponential phases follow one fixed order - that of the Q.K^T MMAs: key tile by key tile,
-            // query tile 0 before query tile 1 - and a phase starts when its predecessor has finished; the other
-            // warpgroup spends that time on the parts that need no exponentials.  `need` = how many phases of the
-            // other warpgroup come before this one in that order (it cannot be more than one phase ahead of that,
-            // since its next phase comes after this one).
-            const int first_other = wk.n_max - wk.n_t[t ^ 1];    // the other tile's first iteration in this item
-            const int it_abs = wk.n_max - n_mine + it;           // this key tile's iteration index in the item
-            const int within = it_abs + t - first_other;         // t = 1 also follows tile 0 of the same iteration
-            const uint32_t need = other_prev + (uint32_t)min(max(within, 0), wk.n_t[t ^ 1]);
-            if (need > 0 && !(ok = wait_bar<false>(bars + Bars::exp_done + 8 * (t ^ 1), (need - 1) & 1, abort_s, P.status, 34))) break;
-          }
           sfp_row[0] = f32x2_to_e4m3x2(sb[0], sb[1]) | (f32x2_to_e4m3x2(sb[2], sb[3]) << 16);     // keys 0-63 of the tile
           sfp_row[128] = f32x2_to_e4m3x2(sb[4], sb[5]) | (f32x2_to_e4m3x2(sb[6], sb[7]) << 16);   // keys 64-127
           l += exp_quantise_store<kPacked>(s, c, neg_e, sb, p_row, swz, P.slot_first);
-          if (kExpTurns) mbar_arrive(bars + Bars::exp_done + 8 * t);
+          if (rescale) {
+            if (!(ok = wait_bar<false>(bar_pv, (sc - 1) & 1, abort_s, P.status, 32))) break;
+            tc_fence_after();
+            const float2 al2 = make_float2(alpha, alpha);
+            // the whole O row at once (the score registers are free by now): all loads in flight together, one
+            // wait, then scale and store - a chunk-by-chunk round trip would expose the tensor-memory latency 8 times
+            uint32_t o[D];
+#pragma unroll
+            for (int ch = 0; ch < D / 32; ++ch) tmem_ld32(tm_O + 32 * ch, *reinterpret_cast<uint32_t (*)[32]>(&o[32 * ch]));
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < D / 2; ++i) {
+              const float2 x = ffma2(make_float2(__uint_as_float(o[2 * i]), __uint_as_float(o[2 * i + 1])), al2,
+                                     make_float2(0.f, 0.f));
+              o[2 * i] = __float_as_uint(x.x); o[2 * i + 1] = __float_as_uint(x.y);
+            }
+#pragma unroll
+            for (int ch = 0; ch < D / 16; ++ch) tmem_st16(tm_O + 16 * ch, *reinterpret_cast<const uint32_t (*)[16]>(&o[16 * ch]));
+            tmem_wait_st();
+          }
           // P^ written (and O_t rescaled if it had to be): hand the tile to the PV issuer
           tc_fence_before();
           fence_proxy_async_smem();

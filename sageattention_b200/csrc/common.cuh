@@ -172,6 +172,13 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
   return false;
 }
 
+// The same for a whole warp that goes on to warp-wide instructions (tcgen05.ld / st, votes): every lane gets the
+// same answer, so the warp never splits on a wait that ran out for some of its lanes only.
+template <bool kHinted, uint32_t kPolls = (1u << 21)>
+__device__ __forceinline__ bool wait_bar_warp(uint32_t bar, uint32_t parity, volatile int* abort_s, int* status, int code) {
+  return __all_sync(0xffffffffu, wait_bar<kHinted, kPolls>(bar, parity, abort_s, status, code));
+}
+
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

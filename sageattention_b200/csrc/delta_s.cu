@@ -40,7 +40,7 @@ struct KDsParams {
 };
 
 template <int D>
-__global__ void __launch_bounds__(kThreads, 2) k_quant_delta_s_kernel(const KDsParams P) {
+__global__ void __launch_bounds__(kThreads, 3) k_quant_delta_s_kernel(const KDsParams P) {
   constexpr int CH = D / 8, RPP = kThreads / CH, NP = kTile / RPP;
   constexpr uint32_t kTileBytes = CH * kChunk;
   extern __shared__ __align__(16) uint8_t dyn_smem[];
@@ -110,63 +110,69 @@ __global__ void __launch_bounds__(kThreads, 2) k_quant_delta_s_kernel(const KDsP
   const int Nk_pad = P.Tk * kTile;
   uint32_t iter = 0;
   bool ok = true;
-  for (int hg = 0; hg < G && ok; ++hg) {
-    const int hq = hkv * G + hg;
+  // rounds = (query head of the group, block of 128 query blocks); the A tile of the next round is fetched into
+  // registers while the current round's MMA runs and its result is written out
+  const int rounds = G * n_mb;
+  auto load_a = [&](uint4 (&a)[NP], const int round) {
+    const int hq = hkv * G + round / n_mb, mb = round % n_mb;
     const __nv_bfloat16* qm_h = P.qm + ((int64_t)b * P.Hq + hq) * P.Tq * D;
+#pragma unroll
+    for (int p = 0; p < NP; ++p) {
+      const int m = mb * 128 + p * RPP + rl;
+      a[p] = m < P.Tq ? __ldg(reinterpret_cast<const uint4*>(qm_h + (int64_t)m * D + c * 8)) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  uint4 a_next[NP];
+  load_a(a_next, 0);
+  for (int round = 0; round < rounds && ok; ++round, ++iter) {
+    const int hq = hkv * G + round / n_mb, mb = round % n_mb;
     __nv_bfloat16* ds_h = P.ds + ((int64_t)b * P.Hq + hq) * P.Tq * Nk_pad + tile * kTile;
-    for (int mb = 0; mb < n_mb && ok; ++mb, ++iter) {
-      // A: block means of query blocks mb*128 ... +127 (zeros beyond the last one)
+    // A: block means of query blocks mb*128 ... +127 (zeros beyond the last one)
 #pragma unroll
-      for (int p = 0; p < NP; ++p) {
-        const int row = p * RPP + rl, m = mb * 128 + row;
-        const uint4 v = m < P.Tq ? __ldg(reinterpret_cast<const uint4*>(qm_h + (int64_t)m * D + c * 8)) : make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(sA + c * kChunk + (row >> 3) * 128 + (row & 7) * 16) = v;
-      }
-      fence_proxy_async_smem();
-      __syncthreads();
-      if (t == 0) {
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)            // K = 16 per instruction = two chunks
-          tc_mma_bf16(tmem, a_lo + kk * (2 * kChunk >> 4), HI, b_lo + kk * (2 * kChunk >> 4), HI, idesc, kk > 0 ? 1u : 0u);
-        tc_commit(bar);
-      }
-      // bounded: a few microseconds normally; gives up after about a second
-      if (P.status != nullptr) {
-        ok = wait_bar<false, (1u << 19)>(bar, iter & 1, abort_s, P.status, 50);
-      } else {
-        ok = mbar_wait(bar, iter & 1, 1u << 19);
-      }
-      ok = __all_sync(0xffffffffu, ok);                // the tensor-memory loads below are warp-wide
+    for (int p = 0; p < NP; ++p) {
+      const int row = p * RPP + rl;
+      *reinterpret_cast<uint4*>(sA + c * kChunk + (row >> 3) * 128 + (row & 7) * 16) = a_next[p];
+    }
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (t == 0) {
       tc_fence_after();
-      if (ok) {
-        // lane = query block, 64 columns (keys) per thread: warps 0-3 take keys 0-63, warps 4-7 keys 64-127
-        const int m = mb * 128 + (warp & 3) * 32 + lane;
-        const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(warp >> 2) * 64;
-        uint32_t r0[32], r1[32];
-        tmem_ld32(taddr, r0);
-        tmem_ld32(taddr + 32, r1);
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk)              // K = 16 per instruction = two chunks
+        tc_mma_bf16(tmem, a_lo + kk * (2 * kChunk >> 4), HI, b_lo + kk * (2 * kChunk >> 4), HI, idesc, kk > 0 ? 1u : 0u);
+      tc_commit(bar);
+    }
+    if (round + 1 < rounds) load_a(a_next, round + 1);
+    // bounded: a few microseconds normally; gives up after about a second
+    if (P.status != nullptr) {
+      ok = wait_bar_warp<false, (1u << 19)>(bar, iter & 1, abort_s, P.status, 50);
+    } else {
+      ok = __all_sync(0xffffffffu, mbar_wait(bar, iter & 1, 1u << 19));
+    }
+    tc_fence_after();
+    if (ok) {
+      // lane = query block, 64 columns (keys) per thread in two halves: warps 0-3 take keys 0-63, warps 4-7 keys 64-127
+      const int m = mb * 128 + (warp & 3) * 32 + lane;
+      const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(warp >> 2) * 64;
+      uint4* dst = reinterpret_cast<uint4*>(ds_h + (int64_t)m * Nk_pad + (warp >> 2) * 64);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t r[32];
+        tmem_ld32(taddr + 32 * half, r);
         tmem_wait_ld();
         if (m < P.Tq) {
-          uint4* dst = reinterpret_cast<uint4*>(ds_h + (int64_t)m * Nk_pad + (warp >> 2) * 64);
 #pragma unroll
           for (int i = 0; i < 4; ++i)
-            dst[i] = make_uint4(pack_bf16(__uint_as_float(r0[8 * i]), __uint_as_float(r0[8 * i + 1])),
-                                pack_bf16(__uint_as_float(r0[8 * i + 2]), __uint_as_float(r0[8 * i + 3])),
-                                pack_bf16(__uint_as_float(r0[8 * i + 4]), __uint_as_float(r0[8 * i + 5])),
-                                pack_bf16(__uint_as_float(r0[8 * i + 6]), __uint_as_float(r0[8 * i + 7])));
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            dst[4 + i] = make_uint4(pack_bf16(__uint_as_float(r1[8 * i]), __uint_as_float(r1[8 * i + 1])),
-                                    pack_bf16(__uint_as_float(r1[8 * i + 2]), __uint_as_float(r1[8 * i + 3])),
-                                    pack_bf16(__uint_as_float(r1[8 * i + 4]), __uint_as_float(r1[8 * i + 5])),
-                                    pack_bf16(__uint_as_float(r1[8 * i + 6]), __uint_as_float(r1[8 * i + 7])));
+            dst[4 * half + i] = make_uint4(pack_bf16(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1])),
+                                           pack_bf16(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])),
+                                           pack_bf16(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])),
+                                           pack_bf16(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7])));
         }
       }
-      // the accumulator and the A tile are rewritten by the next round; every thread leaves the loop together
-      tc_fence_before();
-      ok = __syncthreads_and(ok);
     }
+    // the accumulator and the A tile are rewritten by the next round; every thread leaves the loop together
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
   }
   if (!ok && t == 0) {
     // the MMAs issued last may still be running: give them time to drain before tensor memory is freed
