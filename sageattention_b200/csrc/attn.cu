@@ -79,7 +79,10 @@ namespace {
 
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
-constexpr int kStages = 3;
+#ifndef SAGE3_STAGES
+#define SAGE3_STAGES 3
+#endif
+constexpr int kStages = SAGE3_STAGES;                   // K / V ring depth
 constexpr int kAttnThreads = 384;
 // Register hand-over (setmaxnreg) moves registers inside the pool the CTA was LAUNCHED with; a request beyond
 // it would block forever, so the split is checked here.  kLaunchRegs is what the compiler allocates under
@@ -364,7 +367,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
   constexpr uint32_t kSwzQK = (D == 128) ? 4u : 6u;        // 64-byte / 32-byte swizzle
   constexpr uint32_t kSboQK = (D == 128) ? 512u : 256u;
   constexpr bool kTmaStore = !SAGE3_VARLEN_BUILD && D == 128;   // see the epilogue
-  constexpr bool kIssuerHint = (D == 64);                  // the MMA issuers of the D=64 kernel do better with the longer park
+  // How the two MMA issuer threads wait (measured, same box): the longer park of a hinted try_wait costs them a
+  // little reaction time per key tile but leaves the sub-partition's issue slots to the softmax warp that shares it:
+  // +9 % on rows of 256 key tiles, -2 to -4 % on rows of 8 to 64 (and D=64 gains at every length).
+  const bool issuer_hint = (D == 64) || P.Tk >= 128;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // swizzled tiles need 1024-byte alignment
   const uint32_t sbase = smem_u32(smem);
@@ -536,17 +542,17 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           for (int it = 0; ok && it < wk.n_max; ++it, ++g) {
             const int j = wk.n_max - 1 - it, s = g % kStages;
             const uint32_t ph = (g / kStages) & 1;
-            if (!(ok = wait_bar<kIssuerHint>(bars + Bars::k_full + 8 * s, ph, abort_s, P.status, 21))) break;
-            if (has_ds && !(ok = wait_bar<kIssuerHint>(bars + Bars::ds_ready + 8 * s, ph, abort_s, P.status, 25))) break;
+            if (!(ok = wait_bar_dyn(bars + Bars::k_full + 8 * s, ph, issuer_hint, abort_s, P.status, 21))) break;
+            if (has_ds && !(ok = wait_bar_dyn(bars + Bars::ds_ready + 8 * s, ph, issuer_hint, abort_s, P.status, 25))) break;
             bool first = true;
 #pragma unroll
             for (int t = 0; t < 2; ++t) {
               if (!ok || j >= wk.n_t[t]) continue;
               // the one score buffer must be free: the softmax warpgroup that got the previous Q.K^T (the other
               // query tile, or this one in the previous key tile) has copied it into registers
-              if (nqk > 0 && !(ok = wait_bar<kIssuerHint>(bars + Bars::s_free, (nqk - 1) & 1, abort_s, P.status, 23))) break;
+              if (nqk > 0 && !(ok = wait_bar_dyn(bars + Bars::s_free, (nqk - 1) & 1, issuer_hint, abort_s, P.status, 23))) break;
               if (it == wk.n_max - wk.n_t[t]) {                    // first key tile of this query tile
-                if (!(ok = wait_bar<kIssuerHint>(bars + Bars::q_full + 8 * t, qn[t] & 1, abort_s, P.status, 20))) break;
+                if (!(ok = wait_bar_dyn(bars + Bars::q_full + 8 * t, qn[t] & 1, issuer_hint, abort_s, P.status, 20))) break;
                 ++qn[t];
                 tc_fence_after();
 #pragma unroll
@@ -598,7 +604,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
             const int j = wk.n_max - 1 - it, s = g % kStages;
             const bool act1 = j < wk.n_t[1];
             // the V stage and its scale factors do not depend on the softmax: fetch them before waiting for P
-            if (!(ok = wait_bar<kIssuerHint>(bars + Bars::v_full + 8 * s, (g / kStages) & 1, abort_s, P.status, 24))) break;
+            if (!(ok = wait_bar_dyn(bars + Bars::v_full + 8 * s, (g / kStages) & 1, issuer_hint, abort_s, P.status, 24))) break;
             tc_fence_after();
 #pragma unroll
             for (int kb = 0; kb < 2; ++kb) tc_cp_sf(tm_sfv + 4 * kb, sfv_lo + s * 64 + kb * 32, HI_SF);
@@ -607,9 +613,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
               const bool act = t == 0 ? (j < wk.n_t[0]) : act1;
               if (!(ok && act)) continue;
               const bool first_tile = it == wk.n_max - wk.n_t[t];
-              if (!(ok = wait_bar<kIssuerHint>(bars + Bars::p_full + 8 * t, pv_cnt[t] & 1, abort_s, P.status, 26))) break;
+              if (!(ok = wait_bar_dyn(bars + Bars::p_full + 8 * t, pv_cnt[t] & 1, issuer_hint, abort_s, P.status, 26))) break;
               if (first_tile) {
-                if (n_epi[t] > 0 && !(ok = wait_bar<kIssuerHint>(bars + Bars::o_free + 8 * t, (n_epi[t] - 1) & 1, abort_s, P.status, 22))) break;
+                if (n_epi[t] > 0 && !(ok = wait_bar_dyn(bars + Bars::o_free + 8 * t, (n_epi[t] - 1) & 1, issuer_hint, abort_s, P.status, 22))) break;
                 ++n_epi[t];
               }
               tc_fence_after();

@@ -172,6 +172,19 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
   return false;
 }
 
+// The same with the flavour of the poll chosen at run time (uniform per kernel launch).
+template <uint32_t kPolls = (1u << 21)>
+__device__ __forceinline__ bool wait_bar_dyn(uint32_t bar, uint32_t parity, const bool hinted, volatile int* abort_s,
+                                             int* status, int code) {
+  for (uint32_t i = 0; i < kPolls; ++i) {
+    if (hinted ? mbar_try_wait<20000>(bar, parity) : mbar_try_wait<0>(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && (*abort_s != 0 || *reinterpret_cast<volatile int*>(status) != 0)) break;
+  }
+  *abort_s = 1;
+  atomicCAS(status, 0, code);
+  return false;
+}
+
 // The same for a whole warp that goes on to warp-wide instructions (tcgen05.ld / st, votes): every lane gets the
 // same answer, so the warp never splits on a wait that ran out for some of its lanes only.
 template <bool kHinted, uint32_t kPolls = (1u << 21)>
