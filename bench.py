@@ -323,6 +323,17 @@ def _ulysses_parity(sa, sd, dist, dev, world, rank):
             "parity_shape": {"B": B, "H": H, "N": n * world, "D": D, "head_chunks": sizes}}
 
 
+def ulysses_head_chunks(hpr):
+    """Heads per rank of every exchange / attention chunk: one head first and last (only the first exchange and the
+    last return are exposed), a short ramp, and the bulk in one large chunk in the middle (every chunk is a launch
+    sequence of its own and a round of the persistent attention kernel with a partly filled tail)."""
+    if hpr <= 3:
+        return [1] * hpr
+    ramp = min(3, (hpr - 2) // 3) if hpr >= 8 else 0
+    mid = hpr - 2 - 2 * ramp
+    return [1] + ([ramp] if ramp else []) + [mid] + ([ramp] if ramp else []) + [1]
+
+
 def run_ulysses_leg(sa, dist, dev, world, rank, steps):
     w = WORKLOADS["ulysses"]
     B, H, N, D = w["B"], w["Hq"], w["N"], w["D"]
@@ -359,12 +370,7 @@ def run_ulysses_leg(sa, dist, dev, world, rank, steps):
     koff = torch.randn((B, 1, H, D), generator=torch.Generator(device=dev).manual_seed(99), device=dev) * w["k_off"]
     k = (torch.randn((B, n, H, D), generator=g, device=dev) + koff).to(torch.bfloat16)
     v = torch.randn((B, n, H, D), generator=g, device=dev).to(torch.bfloat16)
-    # heads per rank in chunks of about a fifth, the first and the last chunk the smallest: only the first exchange
-    # and the last return are exposed
-    per = max(1, hpr // 5)
-    sizes = [per] * (hpr // per)
-    if hpr % per:
-        sizes.insert(len(sizes) // 2, hpr % per)
+    sizes = ulysses_head_chunks(hpr)
     for _ in range(3):
         sd.ulysses_attention(q, k, v, head_chunks=sizes)
     torch.cuda.synchronize()

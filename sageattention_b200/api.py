@@ -413,9 +413,13 @@ def sageattn_from_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: O
     if out is None:
         out = torch.empty_like(q).pin_memory()
     # group sizes: about Hkv / head_chunks heads, but ramping up from one head at the start and down to one at
-    # the end, so that the first kernel starts after a small copy and little is left to copy out after the last
+    # the end, so that the first kernel starts after a small copy and little is left to copy out after the last.
+    # A group should also carry enough bytes (about 96 MB of q, k, v) for its copy to be worth a pipeline stage:
+    # every group costs a few host-side calls, which small problems cannot hide.
+    in_bytes = (q.numel() + k.numel() + v.numel()) * q.element_size()
+    head_chunks = max(1, min(head_chunks, int(in_bytes // (96 << 20)) or 1))
     base = max(1, Hkv // max(1, min(head_chunks, Hkv)))
-    ramp = [n for n in (1, 2, 4) if n < base]
+    ramp = [n for n in (1, 2, 4) if n < base] if head_chunks > 1 else []
     sizes = list(ramp)
     left = Hkv - sum(ramp)
     tail = [n for n in reversed(ramp) if n <= left - base]      # keep at least one full group in the middle

@@ -90,9 +90,14 @@ def _head_to_seq(x: torch.Tensor, world: int, group, async_op: bool = False):
     recv = torch.empty_like(send)
     work = dist.all_to_all_single(recv, send, group=group, async_op=async_op)
 
-    def finish():
-        # recv[p] = my tokens for rank p's heads
-        return recv.permute(1, 2, 0, 3, 4).reshape(B, n, world * h, D)
+    def finish(out: Optional[torch.Tensor] = None):
+        # recv[p] = my tokens for rank p's heads; written straight into `out` [B, n, world*h, D] (a view into the
+        # caller's result is fine) when given, so that the chunks need no concatenation afterwards
+        src = recv.permute(1, 2, 0, 3, 4)                                              # [B, n, P, h, D]
+        if out is None:
+            return src.reshape(B, n, world * h, D)
+        out.unflatten(2, (world, h)).copy_(src)
+        return out
     return work, finish
 
 
@@ -160,11 +165,11 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group=N
             full.append(finish())
         o = attn_fn(full[0], full[1], full[2], tensor_layout="NHD", **kwargs)          # [B, N, n_c, D]
         back.append(_head_to_seq(o, world, group, async_op=True))
-    outs = []
-    for work, finish in back:
+    out = torch.empty_like(q)
+    for c, (work, finish) in enumerate(back):
         waited(work)
-        outs.append(finish())                                                          # [B, n, P*n_c, D] heads in rank order
-    return outs[0] if len(outs) == 1 else torch.cat(outs, dim=2)
+        finish(out[:, :, starts[c]:starts[c] + world * sizes[c]])                      # heads in rank order = global order
+    return out
 
 
 def merge_partial(out_a: torch.Tensor, lse_a: torch.Tensor, out_b: torch.Tensor, lse_b: torch.Tensor):
