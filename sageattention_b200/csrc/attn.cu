@@ -52,6 +52,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "tensor_map.h"
 
 // This file is compiled twice: as it is for dense batches, and once more through attn_varlen.cu with
 // SAGE3_VARLEN_BUILD = 1 for variable-length batches (per-sequence offsets and lengths from cu_seqlens).  The
@@ -885,22 +886,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
 // ------------------------------------------------------------------------------------------------
 // host: tensor maps + launch
 // ------------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
-}
-
 // 2-D byte tensor [rows][row_bytes], box = [box_rows][row_bytes]
 bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint32_t row_bytes, uint32_t box_rows,
               CUtensorMapSwizzle swz) {

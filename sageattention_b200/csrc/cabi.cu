@@ -131,6 +131,7 @@ static int quant_qkv_impl(const sage3_quant_args* a, const int* cu_q, const int*
   }
 
   // with delta_s requested, K is quantised by the delta_s kernel, which has the smoothed tile in hand anyway
+  if (a->delta_s != nullptr && !aligned16(a->delta_s)) return SAGE3_ERR_ARGUMENT;     // written through a tensor map
   const bool k_in_ds = a->delta_s != nullptr && a->k.ptr != nullptr;
   if (a->delta_s != nullptr && (!a->q.ptr || !a->k.ptr || a->per_block_mean < 0)) return SAGE3_ERR_ARGUMENT;
   sage3::QuantArgs q{};

@@ -202,6 +202,10 @@ __device__ __forceinline__ void tma_store_4d(const void* tmap, uint32_t src, int
   asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%1, %2, %3, %4}], [%5];"
                :: "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(w), "r"(src) : "memory");
 }
+__device__ __forceinline__ void tma_store_3d(const void* tmap, uint32_t src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+               :: "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(src) : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // all bulk groups of this thread have finished READING shared memory (their source may be reused)
 __device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }

@@ -12,15 +12,19 @@
 // same device function as the fused quantisation kernel, so codes and scales are bit-identical) and laid out
 // in shared memory as the B operand of tcgen05.mma kind::f16; the Q block means of every query head of the GQA
 // group (rows of A, 128 query blocks at a time) are multiplied against it with the accumulator in tensor
-// memory, and every thread writes 128 contiguous bytes of a delta_s row.  HBM-bound: the output
-// ([Tq x 128] bf16 per CTA and query head) dominates the traffic.
+// memory; the [128 query blocks x 128 keys] result goes as bf16 through a swizzled staging tile in shared memory
+// and leaves with two TMA stores (whole 128-byte lines; rows beyond the last query block are clipped by the
+// tensor map).  HBM-bound: the output ([Tq x 128] bf16 per CTA and query head) dominates the traffic.
 //
 // Operand layout in shared memory (K-major, no swizzle): 8-row x 16-byte core matrices; the 16 row groups of one
 // 8-channel chunk are contiguous (128 B apart), chunks are kChunk bytes apart - 16 bytes more than their size so
 // that the 16 lanes which write one row's chunks hit different banks.
+#include <cuda.h>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "quant_rows.cuh"
+#include "tensor_map.h"
 
 namespace sage3 {
 
@@ -39,13 +43,18 @@ struct KDsParams {
   int d_in;                                            // channels the K rows really have; the rest are zero
 };
 
+constexpr int kDsStageBytes = 2 * 128 * 128;          // output staging: [2 key halves][128 rows x 128 bytes], 128-byte swizzle
+
 template <int D>
-__global__ void __launch_bounds__(kThreads, 3) k_quant_delta_s_kernel(const KDsParams P) {
+__global__ void __launch_bounds__(kThreads, 2) k_quant_delta_s_kernel(const __grid_constant__ CUtensorMap tm_ds,
+                                                                      const KDsParams P) {
   constexpr int CH = D / 8, RPP = kThreads / CH, NP = kTile / RPP;
   constexpr uint32_t kTileBytes = CH * kChunk;
-  extern __shared__ __align__(16) uint8_t dyn_smem[];
-  uint8_t* sB = dyn_smem;                              // smoothed K tile  [CH][kChunk]
-  uint8_t* sA = dyn_smem + kTileBytes;                 // 128 Q block means [CH][kChunk]
+  extern __shared__ uint8_t dyn_raw[];
+  uint8_t* dyn_smem = dyn_raw + ((1024u - (smem_u32(dyn_raw) & 1023u)) & 1023u);   // the swizzled staging tile needs it
+  uint8_t* stage = dyn_smem;                           // output staging (first: 1024-byte aligned)
+  uint8_t* sB = dyn_smem + kDsStageBytes;              // smoothed K tile  [CH][kChunk]
+  uint8_t* sA = sB + kTileBytes;                       // 128 Q block means [CH][kChunk]
   uint8_t* sf_smem = sA + kTileBytes;                  // 2048 B
   uint8_t* misc = sf_smem + 2048;                      // mbarrier (8 B), tensor-memory slot (4 B), abort flag (4 B)
   const uint32_t bar = smem_u32(misc), slot = smem_u32(misc + 8);
@@ -107,7 +116,6 @@ __global__ void __launch_bounds__(kThreads, 3) k_quant_delta_s_kernel(const KDsP
   const uint32_t a_lo = (smem_u32(sA) >> 4) | ((kChunk >> 4) << 16);    // leading (K) offset = one chunk
   const uint32_t b_lo = (smem_u32(sB) >> 4) | ((kChunk >> 4) << 16);
   const int n_mb = (P.Tq + 127) / 128;
-  const int Nk_pad = P.Tk * kTile;
   uint32_t iter = 0;
   bool ok = true;
   // rounds = (query head of the group, block of 128 query blocks); the A tile of the next round is fetched into
@@ -126,13 +134,13 @@ __global__ void __launch_bounds__(kThreads, 3) k_quant_delta_s_kernel(const KDsP
   load_a(a_next, 0);
   for (int round = 0; round < rounds && ok; ++round, ++iter) {
     const int hq = hkv * G + round / n_mb, mb = round % n_mb;
-    __nv_bfloat16* ds_h = P.ds + ((int64_t)b * P.Hq + hq) * P.Tq * Nk_pad + tile * kTile;
     // A: block means of query blocks mb*128 ... +127 (zeros beyond the last one)
 #pragma unroll
     for (int p = 0; p < NP; ++p) {
       const int row = p * RPP + rl;
       *reinterpret_cast<uint4*>(sA + c * kChunk + (row >> 3) * 128 + (row & 7) * 16) = a_next[p];
     }
+    if (t == 0) bulk_wait_read0();                     // the previous round's stores have left the staging tile
     fence_proxy_async_smem();
     __syncthreads();
     if (t == 0) {
@@ -151,29 +159,39 @@ __global__ void __launch_bounds__(kThreads, 3) k_quant_delta_s_kernel(const KDsP
     }
     tc_fence_after();
     if (ok) {
-      // lane = query block, 64 columns (keys) per thread in two halves: warps 0-3 take keys 0-63, warps 4-7 keys 64-127
-      const int m = mb * 128 + (warp & 3) * 32 + lane;
-      const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(warp >> 2) * 64;
-      uint4* dst = reinterpret_cast<uint4*>(ds_h + (int64_t)m * Nk_pad + (warp >> 2) * 64);
+      // lane = query block (row of the staging tile), 64 keys per thread: warps 0-3 the tile's keys 0-63, warps 4-7
+      // keys 64-127 (= the two 128-byte-wide store boxes)
+      const int row = (warp & 3) * 32 + lane, half = warp >> 2;
+      const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)half * 64;
+      uint8_t* srow = stage + half * (128 * 128) + row * 128;
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      for (int part = 0; part < 2; ++part) {
         uint32_t r[32];
-        tmem_ld32(taddr + 32 * half, r);
+        tmem_ld32(taddr + 32 * part, r);
         tmem_wait_ld();
-        if (m < P.Tq) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
-            dst[4 * half + i] = make_uint4(pack_bf16(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1])),
-                                           pack_bf16(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])),
-                                           pack_bf16(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])),
-                                           pack_bf16(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7])));
-        }
+        for (int i = 0; i < 4; ++i)
+          *reinterpret_cast<uint4*>(srow + (((4 * part + i) ^ (row & 7)) << 4)) =
+              make_uint4(pack_bf16(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1])),
+                         pack_bf16(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])),
+                         pack_bf16(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])),
+                         pack_bf16(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7])));
       }
+      fence_proxy_async_smem();
+    }
+    tc_fence_before();
+    __syncthreads();                                   // the staging tile is complete (and the accumulator read)
+    if (ok && t == 0) {
+      const int z = b * P.Hq + hq;
+      tma_store_3d(&tm_ds, smem_u32(stage), tile * kTile, mb * 128, z);
+      tma_store_3d(&tm_ds, smem_u32(stage) + 128 * 128, tile * kTile + 64, mb * 128, z);
+      bulk_commit_group();
     }
     // the accumulator and the A tile are rewritten by the next round; every thread leaves the loop together
     tc_fence_before();
     ok = __syncthreads_and(ok);
   }
+  if (t == 0) bulk_wait_read0();                       // the last stores have read the staging tile before the CTA ends
   if (!ok && t == 0) {
     // the MMAs issued last may still be running: give them time to drain before tensor memory is freed
     mbar_wait(bar, iter & 1, 1u << 16);
@@ -195,14 +213,28 @@ cudaError_t launch_delta_s(const DeltaSArgs& a, cudaStream_t stream) {
   P.cu_k = a.cu_k;
   P.d_in = (a.d_in > 0 && a.d_in <= a.D) ? a.d_in : a.D;
   dim3 grid(P.Tk, a.B * a.Hkv);
-  const int smem = 2 * (a.D / 8) * (int)kChunk + 2048 + 16;
+  // delta_s as a 3-D bf16 tensor (key, query block, batch x query head); store boxes of 64 keys x 128 query blocks
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return cudaErrorInvalidValue;
+  CUtensorMap tm;
+  {
+    const cuuint64_t nk_pad = (cuuint64_t)P.Tk * kTile;
+    cuuint64_t dims[3] = {nk_pad, (cuuint64_t)a.Tq, (cuuint64_t)a.B * a.Hq};
+    cuuint64_t strides[2] = {nk_pad * 2, nk_pad * 2 * (cuuint64_t)a.Tq};
+    cuuint32_t box[3] = {64, 128, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    if (enc(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a.ds, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return cudaErrorInvalidValue;
+  }
+  const int smem = kDsStageBytes + 2 * (a.D / 8) * (int)kChunk + 2048 + 16 + 1024;
   // per device and cheap, so set on every call rather than cached per process
   cudaError_t e = a.D == 128
       ? cudaFuncSetAttribute(k_quant_delta_s_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
       : cudaFuncSetAttribute(k_quant_delta_s_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  if (a.D == 128) k_quant_delta_s_kernel<128><<<grid, kThreads, smem, stream>>>(P);
-  else            k_quant_delta_s_kernel<64><<<grid, kThreads, smem, stream>>>(P);
+  if (a.D == 128) k_quant_delta_s_kernel<128><<<grid, kThreads, smem, stream>>>(tm, P);
+  else            k_quant_delta_s_kernel<64><<<grid, kThreads, smem, stream>>>(tm, P);
   return cudaGetLastError();
 }
 

@@ -66,6 +66,11 @@ def test_kernel_matches_oracle_on_same_operands(B, Hq, Hkv, Nq, Nk, D, causal):
     assert cos >= COS_MIN and l1 <= REL_L1_MAX, (cos, l1)
     fin = torch.isfinite(want_lse)
     assert torch.allclose(lse.cpu()[fin], want_lse[fin], atol=2e-3, rtol=1e-4)
+    # rows that see no key (causal, more queries than keys): one sentinel, -inf, whether the whole query tile or only
+    # the row is without keys - what an LSE merge over key shards expects
+    assert bool(torch.isneginf(lse.cpu()[~fin]).all())
+    if causal and Nq > Nk:
+        assert int((~fin).sum()) == B * Hq * (Nq - Nk)
 
 
 @pytest.mark.parametrize("B,Hq,Hkv,Nq,Nk,D,causal", CASES[:10])
