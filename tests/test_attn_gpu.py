@@ -292,3 +292,18 @@ def test_head_dims_other_than_64_and_128_are_zero_padded(D, layout, causal):
     cos, l1 = sage3.accuracy(hnd(out).float().cpu(), emu[..., :D].float())
     assert cos >= COS_MIN and l1 <= REL_L1_MAX, (cos, l1)
     assert torch.allclose(lse.cpu(), emu_lse, atol=5e-3, rtol=1e-4)
+
+
+def test_sdpa_hook_runs_the_fp4_operator_on_the_gpu():
+    """hooks.as_sdpa / patched_sdpa: bf16 CUDA tensors without a mask go to the FP4 operator (same bits as a direct
+    call), anything else to PyTorch's own function."""
+    import torch.nn.functional as F
+    from sageattention_b200 import hooks
+    q, k, v = U.make_qkv(1, 4, 4, 300, 300, 128, seed=8, device=DEV)
+    want = sa.sageattn(q, k, v, is_causal=True)
+    with hooks.patched_sdpa():
+        got = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        masked = F.scaled_dot_product_attention(q, k, v, attn_mask=torch.ones(300, 300, dtype=torch.bool, device=DEV))
+    assert torch.equal(got, want)
+    ref = F.scaled_dot_product_attention(q, k, v)
+    assert torch.allclose(masked.float(), ref.float(), atol=2e-2)      # went to PyTorch: an all-true mask changes nothing
