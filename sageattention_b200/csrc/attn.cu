@@ -80,9 +80,6 @@ namespace {
 
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
-#ifndef SAGE3_SPLIT_LOAD
-#define SAGE3_SPLIT_LOAD 0
-#endif
 #ifndef SAGE3_STAGES
 #define SAGE3_STAGES 3
 #endif
@@ -698,23 +695,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           tc_fence_after();
           uint32_t s[128];
           float bm[8];
-#if SAGE3_SPLIT_LOAD
-          // first half of the row, then the second half in flight while the block maxima of the first are taken
-          const bool early_max = !kPacked && !need_mask;
-          tmem_ld32(tm_S, *reinterpret_cast<uint32_t (*)[32]>(&s[0]));
-          tmem_ld32(tm_S + 32, *reinterpret_cast<uint32_t (*)[32]>(&s[32]));
-          tmem_wait_ld();
-          tmem_ld32(tm_S + 64, *reinterpret_cast<uint32_t (*)[32]>(&s[64]));
-          tmem_ld32(tm_S + 96, *reinterpret_cast<uint32_t (*)[32]>(&s[96]));
-          if (early_max) {
-#pragma unroll
-            for (int blk = 0; blk < 4; ++blk) bm[blk] = max16(&s[16 * blk]);
-          }
-          tmem_wait_ld();
-#else
-          constexpr bool early_max = false;
           load_scores(tm_S, s);
-#endif
           // the scores are in registers: the Q.K^T of the other query tile may overwrite the buffer
           tc_fence_before();
           mbar_arrive(bars + Bars::s_free);
@@ -747,7 +728,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           }
 #pragma unroll
           for (int blk = 0; blk < 8; ++blk)
-            if (!(early_max && blk < 4)) bm[blk] = max16(&s[16 * blk]);
+            bm[blk] = max16(&s[16 * blk]);
           const float m_loc = fmax3(fmax3(bm[0], bm[1], bm[2]), fmax3(bm[3], bm[4], bm[5]), fmaxf(bm[6], bm[7]));
           // O_t *= alpha for the rows whose reference maximum moves, in place in tensor memory - but only after this
           // tile's exponentials (below): by then the P.V of the previous key tile, which must land first, has long
