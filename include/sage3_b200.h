@@ -125,6 +125,11 @@ typedef struct {
                                 score of a row (the pattern of sageattention/core.py:993-994)         */
   int32_t out_head_dim;      /* 0 or shape.D: `out` rows have shape.D columns.  Otherwise a multiple of 8
                                 below shape.D: only that many columns are written (core.py:990)      */
+  int32_t sm_margin;         /* >= 0: SMs to leave to kernels that run at the same time (a collective's).
+                                The attention kernel is persistent, one CTA per SM, with a static work
+                                list: a CTA that finds its SM taken starts late and finishes late.  It
+                                launches min(work items, SMs - sm_margin) CTAs; results do not depend
+                                on it.  The reference has no counterpart.                            */
 } sage3_attn_args;
 
 typedef struct {
@@ -146,6 +151,7 @@ typedef struct {
   int32_t head_dim;          /* 0 or shape.D, else the real head dim of q, k, v and out (a multiple of 8
                                 below shape.D, see sage3_quant_args.head_dim_in); the default softmax
                                 scale is then head_dim^-0.5 (core.py:941)                            */
+  int32_t sm_margin;         /* as in sage3_attn_args                                                */
 } sage3_fwd_args;
 
 /* K-packing mode of the fork ("SageAttention4", api.py:122-177, 193-203): every 15 key tokens become 16 key

@@ -50,7 +50,8 @@ class AttnArgs(C.Structure):
                 ("out", C.c_void_p), ("out_stride_b", C.c_int64), ("out_stride_h", C.c_int64),
                 ("out_stride_n", C.c_int64),
                 ("lse", C.c_void_p), ("sm_scale", C.c_float), ("is_causal", C.c_int32),
-                ("device_status", C.c_void_p), ("lse_add", C.c_void_p), ("out_head_dim", C.c_int32)]
+                ("device_status", C.c_void_p), ("lse_add", C.c_void_p), ("out_head_dim", C.c_int32),
+                ("sm_margin", C.c_int32)]
 
 
 class FwdArgs(C.Structure):
@@ -60,7 +61,7 @@ class FwdArgs(C.Structure):
                 ("lse", C.c_void_p), ("km_out", C.c_void_p), ("sm_scale", C.c_float), ("is_causal", C.c_int32),
                 ("per_block_mean", C.c_int32), ("smooth_k", C.c_int32),
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("device_status", C.c_void_p),
-                ("head_dim", C.c_int32)]
+                ("head_dim", C.c_int32), ("sm_margin", C.c_int32)]
 
 
 class PackArgs(C.Structure):

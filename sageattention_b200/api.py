@@ -150,9 +150,11 @@ def quantize_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layou
 
 
 def fp4_attention(qz: QuantizedQKV, sm_scale: Optional[float] = None, is_causal: bool = False,
-                  tensor_layout: str = "HND", return_lse: bool = False, check_status: bool = False):
+                  tensor_layout: str = "HND", return_lse: bool = False, check_status: bool = False,
+                  sm_margin: int = 0):
     """Attention on quantised operands (``blockscaled_fp4_attn``, ``sageattn4/api.py:231-243`` ->
-    ``mha_fwd``, ``blackwell/api.cpp:258``)."""
+    ``mha_fwd``, ``blackwell/api.cpp:258``).  ``sm_margin``: SMs to leave to kernels that run at the same time
+    (see :func:`sageattn3_blackwell`)."""
     lib = _lib.load()
     B, Hq, Hkv, Nq, Nk, D = qz.shape
     dev = qz.q_codes.device
@@ -177,6 +179,7 @@ def fp4_attention(qz: QuantizedQKV, sm_scale: Optional[float] = None, is_causal:
     a.lse = lse.data_ptr() if lse is not None else None
     a.sm_scale, a.is_causal = float(sm_scale), int(bool(is_causal))
     a.device_status = status.data_ptr()
+    a.sm_margin = int(sm_margin)
     with torch.cuda.device(dev):
         if qz.k_lambda is not None:
             a.shape = _lib.Shape(B, Hq, Hkv, Nq, int(qz.nk_slots), D)
@@ -257,7 +260,7 @@ def sageattn4_blackwell(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tenso
 def sageattn3_blackwell(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",
                         is_causal: bool = False, sm_scale: Optional[float] = None, per_block_mean: bool = True,
                         return_lse: bool = False, smooth_k: bool = True, attn_mask=None,
-                        check_status: bool = False, **kwargs):
+                        check_status: bool = False, sm_margin: int = 0, **kwargs):
     """FP4 attention, drop-in for ``sageattn4_blackwell`` (``sageattn4/api.py:250-288``) with the wider
     argument set of ``sageattn`` (``sageattention/core.py:79-88``).
 
@@ -266,6 +269,11 @@ def sageattn3_blackwell(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tenso
     ``sageattention/core.py:925-937``).  Returns a tensor shaped like q (and the natural-log LSE ``[B,Hq,Nq]`` of
     ``sm_scale * q.k`` when ``return_lse``; ``-inf`` for rows that see no key).  Causal masking is bottom-right
     aligned when Nq != Nk.
+
+    ``sm_margin`` (no counterpart in the reference): the attention kernel is persistent with one CTA per SM and a
+    static work list, so a CTA whose SM is held by another kernel - a collective running beside it on another
+    stream - starts late and the whole launch ends late.  With ``sm_margin = m`` it launches on ``SMs - m`` SMs
+    only; the result is the same bit for bit.
     """
     if attn_mask is not None:
         raise NotImplementedError("attn_mask is not supported (the reference ignores it as well)")
@@ -295,7 +303,7 @@ def sageattn3_blackwell(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tenso
         q, k, v = (torch.nn.functional.pad(t, (0, pad)) for t in (q, k, v))
         res = sageattn3_blackwell(q, k, v, tensor_layout=tensor_layout, is_causal=is_causal, sm_scale=sm_scale,
                                   per_block_mean=per_block_mean, return_lse=return_lse, smooth_k=smooth_k,
-                                  check_status=check_status)
+                                  check_status=check_status, sm_margin=sm_margin)
         return (res[0][..., :d_og].contiguous(), res[1]) if return_lse else res[..., :d_og].contiguous()
     if D not in (64, 128):
         D = 64 if D < 64 else 128
@@ -318,6 +326,7 @@ def sageattn3_blackwell(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tenso
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
     a.device_status = status.data_ptr()
     a.head_dim = d_og if d_og != D else 0
+    a.sm_margin = int(sm_margin)
     with torch.cuda.device(dev):
         _lib.check(lib.sage3_attention(C.byref(a), _stream_ptr(dev)), "sage3_attention")
         if check_status:

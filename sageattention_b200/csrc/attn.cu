@@ -979,7 +979,8 @@ cudaError_t launch(const AttnArgs& a, cudaStream_t stream) {
     if (dev >= 0 && dev < 64) __atomic_store_n(&ready[dev], 1, __ATOMIC_RELEASE);
   }
   const int64_t work = (int64_t)a.B * a.Hq * ((Tq + 1) / 2);
-  const int64_t grid = work < sms ? work : sms;
+  const int64_t ctas = sms - a.sm_margin > 1 ? sms - a.sm_margin : 1;
+  const int64_t grid = work < ctas ? work : ctas;
   kern<<<(unsigned)grid, kAttnThreads, L::total + 1024, stream>>>(tq, tk, tv, to, P);
   return cudaGetLastError();
 }

@@ -184,6 +184,7 @@ static int attn_fwd_impl(const sage3_attn_args* a, const float* k_lambda, const 
   if (a->delta_s && a->delta_s_rows != 1 && a->delta_s_rows != Tq) return SAGE3_ERR_ARGUMENT;
   if (!(a->sm_scale > 0.f)) return SAGE3_ERR_ARGUMENT;          // the row maximum is tracked in raw score units
   if (!head_dim_ok(a->out_head_dim, s.D)) return SAGE3_ERR_ARGUMENT;
+  if (a->sm_margin < 0) return SAGE3_ERR_ARGUMENT;
   cudaStream_t stream = (cudaStream_t)stream_;
   cudaError_t e = cudaSuccess;
   if (zero_status) {
@@ -200,6 +201,7 @@ static int attn_fwd_impl(const sage3_attn_args* a, const float* k_lambda, const 
   k.k_lambda = k_lambda;
   k.slot_first = slot_first;
   k.d_out = a->out_head_dim;
+  k.sm_margin = a->sm_margin;
   k.cu_q = cu_q; k.cu_k = cu_k;
   e = (cu_q != nullptr || cu_k != nullptr) ? sage3::launch_attn_fwd_varlen(k, stream) : sage3::launch_attn_fwd(k, stream);
   if (e != cudaSuccess) return cuda_fail(e);
@@ -300,6 +302,7 @@ int sage3_attention(const sage3_fwd_args* a, void* stream) {
   t.lse = a->lse; t.sm_scale = sm_scale; t.is_causal = a->is_causal; t.device_status = status;
   t.lse_add = q.q_dot_km;
   t.out_head_dim = a->head_dim;
+  t.sm_margin = a->sm_margin;
   return attn_fwd_impl(&t, nullptr, nullptr, nullptr, stream, 0, /*zero_status=*/false);
 }
 

@@ -74,6 +74,7 @@ struct AttnArgs {
   const float* k_lambda;                  // K-packing mode: fp32 [B,Hkv,Tk*128]; Nk is then the packed length
   int slot_first = 0;                     // K-packing mode: mean slot = first token's score (else masked)
   int d_out = 0;                          // columns the output rows really have (0 = D; <= D, multiple of 8)
+  int sm_margin = 0;                      // SMs left free for kernels running beside the persistent attention kernel
   const int* cu_q = nullptr;              // variable-length batches, see QuantArgs; out is then [tokens, Hq, D]
   const int* cu_k = nullptr;
 };

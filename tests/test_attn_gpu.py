@@ -307,3 +307,17 @@ def test_sdpa_hook_runs_the_fp4_operator_on_the_gpu():
     assert torch.equal(got, want)
     ref = F.scaled_dot_product_attention(q, k, v)
     assert torch.allclose(masked.float(), ref.float(), atol=2e-2)      # went to PyTorch: an all-true mask changes nothing
+
+
+def test_sm_margin_changes_the_grid_but_not_one_bit_of_the_result():
+    """sm_margin leaves SMs to kernels running beside the persistent attention kernel (a collective's): fewer CTAs
+    walk the same work list, every item is computed exactly as before."""
+    q, k, v = U.make_qkv(1, 6, 2, 3000, 3000, 128, seed=31, k_offset_std=2.0, device="cuda")
+    want, want_lse = sa.sageattn3_blackwell(q, k, v, is_causal=True, return_lse=True, check_status=True)
+    for margin in (8, 40, 147, 500):
+        got, lse = sa.sageattn3_blackwell(q, k, v, is_causal=True, return_lse=True, check_status=True, sm_margin=margin)
+        assert torch.equal(got, want) and torch.equal(lse, want_lse), margin
+    qz = sa.quantize_qkv(q, k, v)
+    assert torch.equal(sa.fp4_attention(qz, is_causal=True, sm_margin=16), sa.fp4_attention(qz, is_causal=True))
+    with pytest.raises(RuntimeError):
+        sa.fp4_attention(qz, sm_margin=-1)

@@ -26,6 +26,28 @@ def test_library_exports_every_declared_symbol():
     assert set(names) >= set(_lib.EXPORTS)
 
 
+def test_ctypes_mirrors_have_the_layout_of_the_c_structs(tmp_path):
+    """The Python front end fills ctypes mirrors of the header's structs: sizes and the offset of the last field must
+    be what a C compiler makes of the header (a field added on one side only would shift everything behind it)."""
+    import subprocess
+    pairs = {"sage3_shape": _lib.Shape, "sage3_tensor": _lib.Tensor, "sage3_sizes": _lib.Sizes,
+             "sage3_quant_args": _lib.QuantArgs, "sage3_attn_args": _lib.AttnArgs, "sage3_fwd_args": _lib.FwdArgs,
+             "sage3_pack_args": _lib.PackArgs, "sage3_varlen_args": _lib.VarlenArgs}
+    lines = "".join(f'  printf("{n} %zu %zu\\n", sizeof({n}), offsetof({n}, {cls._fields_[-1][0]}));\n'
+                    for n, cls in pairs.items())
+    src = tmp_path / "layout.c"
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "sage3_b200.h"\nint main(void) {\n' + lines +
+                   "  return 0;\n}\n")
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", str(HEADER.parent), str(src), "-o", str(exe)], check=True)
+    got = {}
+    for line in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines():
+        name, size, last = line.split()
+        got[name] = (int(size), int(last))
+    for n, cls in pairs.items():
+        assert got[n] == (C.sizeof(cls), getattr(cls, cls._fields_[-1][0]).offset), n
+
+
 def test_version_and_status_strings():
     lib = _lib.load()
     assert lib.sage3_version() >= 100
