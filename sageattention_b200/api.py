@@ -401,10 +401,10 @@ _host_streams = {}
 
 
 def sageattn_from_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[torch.Tensor] = None,
-                       device=None, head_chunks: int = 8, is_causal: bool = False, sm_scale: Optional[float] = None,
+                       device=None, head_chunks=8, is_causal: bool = False, sm_scale: Optional[float] = None,
                        **kwargs) -> torch.Tensor:
     """Attention on HOST tensors (HND ``[B,H,N,D]`` bf16, ideally pinned): the heads are processed in
-    ``head_chunks`` groups of kv heads, and the host-to-device copy of group ``i+1`` and the
+    ``head_chunks`` groups of kv heads (a number, or an explicit list of kv heads per group), and the host-to-device copy of group ``i+1`` and the
     device-to-host copy of group ``i-1`` run on their own streams while group ``i`` is computed (groups
     alternate between two compute streams so that their kernels overlap at the seams), so the
     PCIe transfers hide behind the kernels (or the other way round).  Returns the output as a host tensor
@@ -425,18 +425,23 @@ def sageattn_from_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: O
     # the end, so that the first kernel starts after a small copy and little is left to copy out after the last.
     # A group should also carry enough bytes (about 96 MB of q, k, v) for its copy to be worth a pipeline stage:
     # every group costs a few host-side calls, which small problems cannot hide.
-    in_bytes = (q.numel() + k.numel() + v.numel()) * q.element_size()
-    head_chunks = max(1, min(head_chunks, int(in_bytes // (96 << 20)) or 1))
-    base = max(1, Hkv // max(1, min(head_chunks, Hkv)))
-    ramp = [n for n in (1, 2, 4) if n < base] if head_chunks > 1 else []
-    sizes = list(ramp)
-    left = Hkv - sum(ramp)
-    tail = [n for n in reversed(ramp) if n <= left - base]      # keep at least one full group in the middle
-    left -= sum(tail)
-    while left > 0:
-        sizes.append(min(base, left))
-        left -= sizes[-1]
-    sizes += tail
+    if isinstance(head_chunks, (list, tuple)):
+        sizes = [int(n) for n in head_chunks]                    # explicit group sizes (kv heads per group)
+        if sum(sizes) != Hkv or min(sizes) < 1:
+            raise ValueError(f"head_chunks {sizes} must be positive and add up to the {Hkv} kv heads")
+    else:
+        in_bytes = (q.numel() + k.numel() + v.numel()) * q.element_size()
+        head_chunks = max(1, min(head_chunks, int(in_bytes // (96 << 20)) or 1))
+        base = max(1, Hkv // max(1, min(head_chunks, Hkv)))
+        ramp = [n for n in (1, 2, 4) if n < base] if head_chunks > 1 else []
+        sizes = list(ramp)
+        left = Hkv - sum(ramp)
+        tail = [n for n in reversed(ramp) if n <= left - base]      # keep at least one full group in the middle
+        left -= sum(tail)
+        while left > 0:
+            sizes.append(min(base, left))
+            left -= sizes[-1]
+        sizes += tail
     bounds = [0]
     for n in sizes:
         bounds.append(bounds[-1] + n)
