@@ -31,7 +31,8 @@
 //   warps 0-3   softmax warpgroup of query tile 0: thread r owns score row r (tensor-memory lane r).  Per key
 //               tile it copies its 128 scores from tensor memory into registers and releases the score buffer at
 //               once (the Q.K^T of the other query tile is issued into it while this tile is worked on), then:
-//               16-key block maxima, block scales, exponentials, E2M1 codes of P^ into shared memory.  It never
+//               16-key block maxima, block scales, exponentials, E2M1 codes of P^ into tensor memory (the P.V MMA
+//               takes its A operand from there; only the block scales go through shared memory).  It never
 //               waits for the P.V product: the MMA accumulates into the tile's O in tensor memory.  At the end of
 //               an item O / l goes out as bf16 (D=128: through a swizzled staging tile and TMA stores).
 //   warps 4-7   the same for query tile 1; the two warpgroups settle half a period apart
@@ -44,7 +45,8 @@
 //               touch delta_s
 //   warp 11     PV issuer (one lane): scale-factor copies and P.V MMAs, O_t += P^_t V^
 //
-// Tensor memory (512 columns): O0 [0,D) O1 [D,2D) S [2D,2D+128) and 48 columns of scale factors.
+// Tensor memory (512 columns): O0 [0,D) O1 [D,2D) S [2D,2D+128), 48 columns of scale factors, P^0 and P^1 (16
+// columns each: 128 FP4 codes per row).
 //
 // Every wait on an mbarrier is bounded; if one gives up the CTA records a code in *status, waits
 // (bounded) for its own copies and MMAs in flight, frees its tensor memory and returns.
@@ -113,14 +115,12 @@ struct Smem {
   static constexpr int kQBytes = kBlockM * D / 2;
   static constexpr int kKBytes = kBlockN * D / 2;
   static constexpr int kVBytes = D * kBlockN / 2;
-  static constexpr int kPBytes = kBlockM * kBlockN / 2;
   static constexpr int kSfRow = (D / 64) * 512;          // Q / K scales per tile
   static constexpr int kSfV = 1024;                       // V^T scales per tile
   static constexpr int q = 0;                             // [2]
   static constexpr int k = q + 2 * kQBytes;               // [kStages]
   static constexpr int v = k + kStages * kKBytes;         // [kStages]
-  static constexpr int p = v + kStages * kVBytes;         // [2]  P^ codes, 128 rows x 64 bytes
-  static constexpr int sfq = p + 2 * kPBytes;             // [2][1024]
+  static constexpr int sfq = v + kStages * kVBytes;       // [2][1024]
   static constexpr int sfk = sfq + 2 * 1024;              // [kStages][1024]
   static constexpr int sfv = sfk + kStages * 1024;        // [kStages][1024]
   static constexpr int sfp = sfv + kStages * 1024;        // [2][1024]
@@ -236,15 +236,15 @@ __device__ __forceinline__ void load_scores(const uint32_t tm_S, uint32_t (&s)[1
   tmem_wait_ld();
 }
 
-// P / blockscale = 2^(s*c - (bm*c + log2(1/6))) in [0, 6] -> E2M1 codes into the swizzled P^ tile (64 bytes per
-// row); returns the row sum of the unquantised P = sum over blocks of (sum of P/blockscale) * blockscale
+// P / blockscale = 2^(s*c - (bm*c + log2(1/6))) in [0, 6] -> E2M1 codes into this row's 16 tensor-memory columns of
+// P^ (8 codes per column, in key order - the A operand of the P.V MMA is read from there); returns the row sum of the unquantised P = sum over blocks of (sum of P/blockscale) * blockscale
 // (softmax_fused.h:135-153).  neg_e[b] = -(bm_b*c + log2(1/6)), sb[b] = the block's unrounded scale.
 // K-packing mode with slot_first: the first column of every block is the group's mean slot carrying a copy of the
 // first token's score; its P^ goes to the MMA like any other, but it is no token and stays out of the row sum
 // (softmax_fused.h:48-64).
 template <bool kPacked>
 __device__ __forceinline__ float exp_quantise_store(const uint32_t (&s)[128], const float c, const float (&neg_e)[8],
-                                                    const float (&sb)[8], uint8_t* p_row, const int swz,
+                                                    const float (&sb)[8], const uint32_t tm_P,
                                                     const bool slot_first) {
   const float2 c2 = make_float2(c, c);
   float lsum = 0.f;
@@ -265,7 +265,7 @@ __device__ __forceinline__ float exp_quantise_store(const uint32_t (&s)[128], co
     lsum = fmaf(bsum, sb[blk], lsum);
     code[(blk & 1) * 2 + 0] = f32x8_to_e2m1x8(e[0].x, e[0].y, e[1].x, e[1].y, e[2].x, e[2].y, e[3].x, e[3].y);
     code[(blk & 1) * 2 + 1] = f32x8_to_e2m1x8(e[4].x, e[4].y, e[5].x, e[5].y, e[6].x, e[6].y, e[7].x, e[7].y);
-    if (blk & 1) *reinterpret_cast<uint4*>(p_row + (((blk >> 1) ^ swz) << 4)) = make_uint4(code[0], code[1], code[2], code[3]);
+    if (blk & 1) tmem_st4(tm_P + 4 * (blk >> 1), code[0], code[1], code[2], code[3]);     // 32 keys = 4 columns
   }
   return lsum;
 }
@@ -426,6 +426,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
   // columns: O0 [0, D)  O1 [D, 2D)  S [2D, 2D + 128)  scale factors behind
   const uint32_t tm_Sbuf = tmem + 2 * D;
   const uint32_t tm_sfq = tm_Sbuf + 128, tm_sfk = tm_sfq + 16, tm_sfp = tm_sfk + 8, tm_sfv = tm_sfp + 16;
+  const uint32_t tm_P = tm_sfv + 8;                       // [2] P^ codes: the A operand of the P.V MMAs, 16 columns each
 
   // read once after the barrier: every warp takes the same branch, so the register hand-over
   // below (setmaxnreg) is always executed by whole warpgroups
@@ -595,7 +596,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         constexpr uint32_t HI_PV = (512u >> 4) | (1u << 14) | (4u << 29);
         constexpr uint32_t HI_SF = (128u >> 4) | (1u << 14);
         constexpr uint32_t LBO1 = 1u << 16;
-        const uint32_t p_lo = ((sbase + L::p) >> 4) | LBO1, v_lo = ((sbase + L::v) >> 4) | LBO1;
+        const uint32_t v_lo = ((sbase + L::v) >> 4) | LBO1;
         const uint32_t sfv_lo = (sbase + L::sfv) >> 4, sfp_lo = (sbase + L::sfp) >> 4;
         bool ok = true;
         uint32_t g = 0, pv_cnt[2] = {0, 0}, n_epi[2] = {0, 0};
@@ -624,8 +625,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
               for (int kb = 0; kb < 2; ++kb) tc_cp_sf(tm_sfp + 8 * t + 4 * kb, sfp_lo + t * 64 + kb * 32, HI_SF);
 #pragma unroll
               for (int kb = 0; kb < 2; ++kb)
-                tc_mma_nvf4(tmem + t * D, p_lo + t * (L::kPBytes >> 4) + kb * 2, HI_PV, v_lo + s * (L::kVBytes >> 4) + kb * 2, HI_PV,
-                            idesc_pv, tm_sfp + 8 * t + 4 * kb, tm_sfv + 4 * kb, (first_tile && kb == 0) ? 0u : 1u);
+                tc_mma_nvf4_ta(tmem + t * D, tm_P + 16 * t + 8 * kb, v_lo + s * (L::kVBytes >> 4) + kb * 2, HI_PV,
+                               idesc_pv, tm_sfp + 8 * t + 4 * kb, tm_sfv + 4 * kb, (first_tile && kb == 0) ? 0u : 1u);
               tc_commit(bars + Bars::pv_done + 8 * t);
               ++pv_cnt[t];
               if (t == 1 || !act1) tc_commit(bars + Bars::v_empty + 8 * s);   // last PV of this stage
@@ -646,8 +647,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       const uint32_t tm_S = tm_Sbuf + lane_addr;
       const uint32_t tm_O = tmem + t * D + lane_addr;
       const float c = P.scale_log2;
-      uint8_t* p_row = smem + L::p + t * L::kPBytes + row * 64;
-      const int swz = (row >> 1) & 3;
+      const uint32_t tm_Prow = tm_P + 16 * t + lane_addr;        // this row of P^: 16 columns of 8 codes
       uint32_t* sfp_row = reinterpret_cast<uint32_t*>(smem + L::sfp + t * 1024 + sf_atom_offset(row, 0));
       const uint32_t bar_s = bars + Bars::s_full + 8 * t, bar_p = bars + Bars::p_full + 8 * t;
       const uint32_t bar_pv = bars + Bars::pv_done + 8 * t;
@@ -760,7 +760,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
           if (sc > 0 && !(ok = wait_bar<false>(bar_pv, (sc - 1) & 1, abort_s, P.status, 31))) break;
           sfp_row[0] = f32x2_to_e4m3x2(sb[0], sb[1]) | (f32x2_to_e4m3x2(sb[2], sb[3]) << 16);     // keys 0-63 of the tile
           sfp_row[128] = f32x2_to_e4m3x2(sb[4], sb[5]) | (f32x2_to_e4m3x2(sb[6], sb[7]) << 16);   // keys 64-127
-          l += exp_quantise_store<kPacked>(s, c, neg_e, sb, p_row, swz, P.slot_first);
+          l += exp_quantise_store<kPacked>(s, c, neg_e, sb, tm_Prow, P.slot_first);
           if (rescale) {
             if (!(ok = wait_bar<false>(bar_pv, (sc - 1) & 1, abort_s, P.status, 32))) break;
             tc_fence_after();
@@ -781,7 +781,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
             for (int ch = 0; ch < D / 16; ++ch) tmem_st16(tm_O + 16 * ch, *reinterpret_cast<const uint32_t (*)[16]>(&o[16 * ch]));
             tmem_wait_st();
           }
-          // P^ written (and O_t rescaled if it had to be): hand the tile to the PV issuer
+          // P^ written (and O_t rescaled if it had to be): hand the tile to the PV issuer.  The codes went to tensor
+          // memory (tcgen05.st), their block scales to shared memory for the issuer's tcgen05.cp.
+          tmem_wait_st();
           tc_fence_before();
           fence_proxy_async_smem();
           mbar_arrive(bar_p);
